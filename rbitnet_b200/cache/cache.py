@@ -64,7 +64,7 @@ class SequenceCache:
     """Slots for sequences; keys and values for each cached run of a layer; per-sequence state."""
 
     def __init__(self, cache_needs: Dict[int, CacheNeed], reads: Dict[int, int],
-                 state_needs: Dict[int, StateNeed], max_tokens: int, max_seq: int, dtype, device,
+                 state_needs: Dict[int, object], max_tokens: int, max_seq: int, dtype, device,
                  page_size: int = PAGE_SIZE, n_slots: Optional[int] = None):
         """cache_needs: schedule entry -> need, for entries that write their own keys and values.
         reads: schedule entry -> the entry whose cache it reads.  max_tokens: the most positions
@@ -92,9 +92,15 @@ class SequenceCache:
             self._where[entry] = (g, i, False)
         self.book = SlotBook(self.n_slots, [grp.n_pages for grp in self.groups], page_size, max_seq,
                              windows=[grp.need.window for grp in self.groups])
-        self.states: Dict[int, torch.Tensor] = {
-            entry: torch.zeros((self.n_slots, *need.shape), dtype=need.dtype, device=device)
-            for entry, need in state_needs.items()}
+        # one tensor [n_slots, *shape] per need; a mixer that keeps several tensors per sequence names them,
+        # and those are kept under (entry, name)
+        self.states: Dict[object, torch.Tensor] = {}
+        self._state_names: Dict[int, Optional[list]] = {}
+        for entry, need in state_needs.items():
+            named = need if isinstance(need, dict) else None
+            self._state_names[entry] = list(named) if named is not None else None
+            for key, one in (((entry, n), v) for n, v in named.items()) if named is not None else ((entry, need),):
+                self.states[key] = torch.zeros((self.n_slots, *one.shape), dtype=one.dtype, device=device)
 
     # ---- slots
     def alloc(self) -> int:
@@ -181,8 +187,13 @@ class SequenceCache:
         return CacheLayerView(streams[0], streams[1] if len(streams) > 1 else None, grp.table, self.max_pages,
                               self.page_size, grp.need.n_kv_heads, grp.need.head_dim, writes, g, streams)
 
-    def state(self, entry: int) -> Optional[torch.Tensor]:
-        return self.states.get(entry)
+    def state(self, entry: int):
+        """The state area of a schedule entry: a tensor [n_slots, *shape], a dict name -> tensor for a
+        mixer that declared several, or None."""
+        names = self._state_names.get(entry, None)
+        if names is None:
+            return self.states.get(entry)
+        return {n: self.states[(entry, n)] for n in names}
 
     def bytes(self) -> int:
         return sum(g.bytes() for g in self.groups) + sum(s.numel() * s.element_size()

@@ -1,8 +1,9 @@
 from .base import ModelConfig, ConfigError, read_config_json
 from .llama import LlamaConfig
+from .safuvik import SafuvikConfig
 from .registry import (register_architecture, unregister_architecture, known_architectures,
                        get_architecture, architecture_of, config_from_dict, load_config)
 
-__all__ = ["ModelConfig", "ConfigError", "read_config_json", "LlamaConfig",
+__all__ = ["ModelConfig", "ConfigError", "read_config_json", "LlamaConfig", "SafuvikConfig",
            "register_architecture", "unregister_architecture", "known_architectures",
            "get_architecture", "architecture_of", "config_from_dict", "load_config"]

@@ -1,6 +1,6 @@
 """One registry from an architecture's name to its configuration class and its model builder.
 
-``config.json``'s ``architectures[0]`` chooses the entry, everywhere in the
+``config.json``'s ``architectures[0]`` (or its ``architecture``, a plain name) chooses the entry, everywhere in the
 package (engine, command line, trace replay).  The reference reads the
 architecture name only for display (crates/bitnet-core/src/gguf/parse.rs:222-234)
 and has a single model; here the name is the dispatch key so that a second
@@ -47,6 +47,8 @@ def get_architecture(name: str) -> Architecture:
 
 def architecture_of(config_dict) -> Architecture:
     archs = config_dict.get("architectures")
+    if not archs and isinstance(config_dict.get("architecture"), str):
+        archs = [config_dict["architecture"]]
     if not archs or not isinstance(archs, list):
         raise ConfigError("config.json: missing architectures")
     return get_architecture(archs[0])

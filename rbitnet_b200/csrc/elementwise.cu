@@ -511,4 +511,189 @@ RB_EXPORT int rb_decode_advance(int* token_ids, int* tok_pos, const int* sampled
   return 0;
 }
 
+
+// ---------------------------------------------------------------- norm over a whole projection + rotation of a prefix + cache append
+// Rows of projections [q (H D) | k (Kh D) | v (Kh Dv) | ...].  Per token:
+//   q <- q / rms(q over all H D values) * wq     (likewise k; skipped without weights)
+//   the first rot_dim values of every q and k head turn by the position's angles; cos and sin are
+//   multiplied by `magnitude`; the rest of the head passes;
+//   q goes to q_out[T, H, Dc]; k and v go to the token's place in the paged cache, whose rows are
+//   Dc wide: values behind D (Dv) are written as zeros, so kernels that know one head size serve
+//   keys and values of different sizes.
+// The angle is position * freq in float64, brought into (-pi, pi] before the float32 sine and cosine,
+// so that it does not lose digits at large positions.  freq: rot_dim/2 float64 values.
+__device__ __forceinline__ void rb_angle_sincos(int pos, double freq, float magnitude, float* sn, float* cs) {
+  const double a = (double)pos * freq;
+  const double turns = rint(a * 0.15915494309189535);
+  const float r = (float)fma(-turns, 6.283185307179586, a);
+  sincosf(r, sn, cs);
+  *sn *= magnitude;
+  *cs *= magnitude;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) norm_rotate_append_kernel(
+    T* __restrict__ q_out, const T* __restrict__ proj, int64_t ld, const float* __restrict__ q_norm_w,
+    const float* __restrict__ k_norm_w, float eps, const double* __restrict__ freq, float magnitude,
+    const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, RbPagedLayer cache, int H, int D, int Dv,
+    int rot_dim, int interleaved, int write_kv) {
+  rb_pdl_launch_dependents();
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const int Dc = cache.head_dim, Kh = cache.n_kv_heads;
+  const int pos = tok_pos[t], slot = tok_slot[t];
+  rb_pdl_wait();
+  const T* row = proj + (int64_t)t * ld;
+  float rq = 1.f, rk = 1.f;
+  if (q_norm_w != nullptr) {
+    float ss = 0.f;
+    for (int e = threadIdx.x; e < H * D; e += blockDim.x) { const float v = rb_to_float<T>(row[e]); ss += v * v; }
+    ss = rb_block_sum(ss, scratch);
+    rq = 1.0f / sqrtf(ss / (float)(H * D) + eps);
+  }
+  if (k_norm_w != nullptr && write_kv) {
+    float ss = 0.f;
+    for (int e = threadIdx.x; e < Kh * D; e += blockDim.x) { const float v = rb_to_float<T>(row[H * D + e]); ss += v * v; }
+    ss = rb_block_sum(ss, scratch);
+    rk = 1.0f / sqrtf(ss / (float)(Kh * D) + eps);
+  }
+  const int n_rot_heads = H + (write_kv ? Kh : 0);
+  const int rhalf = rot_dim / 2;
+  T* kdst = (T*)cache.k;
+  T* vdst = (T*)cache.v;
+  // one output value per thread and turn: a q or k head's value (normed, turned or passed), or padding
+  for (int idx = threadIdx.x; idx < n_rot_heads * Dc; idx += blockDim.x) {
+    const int head = idx / Dc, e = idx % Dc;
+    const bool is_q = head < H;
+    T* dst = is_q ? q_out + ((int64_t)t * H + head) * Dc : kdst + rb_page_offset(cache, slot, pos, head - H);
+    if (e >= D) { dst[e] = rb_from_float<T>(0.f); continue; }
+    const int base = head * D;          // q heads, then k heads, are contiguous in a row
+    const float* nw = is_q ? q_norm_w : k_norm_w;
+    const float fac = is_q ? rq : rk;
+    auto value = [&](int i) { const float v = rb_to_float<T>(row[base + i]); return nw != nullptr ? v * fac * nw[base - (is_q ? 0 : H * D) + i] : v; };
+    float y;
+    if (e >= rot_dim) {
+      y = value(e);
+    } else {
+      int pair, other;
+      bool first;
+      if (interleaved) { pair = e >> 1; first = (e & 1) == 0; other = first ? e + 1 : e - 1; }
+      else { first = e < rhalf; pair = first ? e : e - rhalf; other = first ? e + rhalf : e - rhalf; }
+      float sn, cs;
+      rb_angle_sincos(pos, freq[pair], magnitude, &sn, &cs);
+      const float me = value(e), ot = value(other);
+      y = first ? me * cs - ot * sn : me * cs + ot * sn;
+    }
+    dst[e] = rb_from_float<T>(y);
+  }
+  if (write_kv) {
+    const T* vsrc = row + (int64_t)(H + Kh) * D;
+    for (int idx = threadIdx.x; idx < Kh * Dc; idx += blockDim.x) {
+      const int kvh = idx / Dc, e = idx % Dc;
+      vdst[rb_page_offset(cache, slot, pos, kvh) + e] = e < Dv ? vsrc[kvh * Dv + e] : rb_from_float<T>(0.f);
+    }
+  }
+}
+
+// dtype: the type of the projections, of q_out and of the cache.  Dc: the width of q_out's and the cache's heads.
+RB_EXPORT int rb_norm_rotate_append(void* q_out, const void* proj, int64_t ld, int dtype, const float* q_norm_w,
+                                    const float* k_norm_w, float eps, const double* freq, float magnitude,
+                                    const int* tok_pos, const int* tok_slot, void* cache_k, void* cache_v,
+                                    const int* page_table, int max_pages, int page_size, int T, int H, int Kh, int D,
+                                    int Dv, int Dc, int rot_dim, int interleaved, int write_kv, cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(H > 0 && Kh > 0 && D > 0 && Dv > 0 && Dc >= D && Dc >= Dv && page_size > 0,
+             "rb_norm_rotate_append: bad sizes H=%d Kh=%d D=%d Dv=%d cache width %d", H, Kh, D, Dv, Dc);
+  RB_REQUIRE(rot_dim >= 0 && rot_dim <= D && rot_dim % 2 == 0 && (rot_dim == 0 || freq != nullptr),
+             "rb_norm_rotate_append: the rotated prefix %d must be even and at most the head size %d", rot_dim, D);
+  RbPagedLayer c{cache_k, cache_v, page_table, max_pages, page_size, Kh, Dc};
+  if (dtype == RB_F32)
+    RB_LAUNCH("norm_rotate_append_kernel", (norm_rotate_append_kernel<float>), T, 256, 0, stream, (float*)q_out, (const float*)proj, ld, q_norm_w, k_norm_w, eps, freq, magnitude, tok_pos, tok_slot, c, H, D, Dv, rot_dim, interleaved, write_kv);
+  else if (dtype == RB_BF16)
+    RB_LAUNCH("norm_rotate_append_kernel", (norm_rotate_append_kernel<__nv_bfloat16>), T, 256, 0, stream, (__nv_bfloat16*)q_out, (const __nv_bfloat16*)proj, ld, q_norm_w, k_norm_w, eps, freq, magnitude, tok_pos, tok_slot, c, H, D, Dv, rot_dim, interleaved, write_kv);
+  else
+    RB_FAIL("rb_norm_rotate_append: unknown dtype %d", dtype);
+  RB_CHECK_LAUNCH("rb_norm_rotate_append");
+  return 0;
+}
+
+// ---------------------------------------------------------------- a gate per head on the attention's output
+// out[t, h*Dv + j] = a[t, h*Dc + j] * sigmoid(gate[t*ldg + h]) for j < Dv: drops the padding of heads that are
+// Dc wide and applies one gate value per head (no gate: gate == null).
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ gate, int64_t ldg,
+                                 int64_t n, int H, int Dv, int Dc) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / ((int64_t)H * Dv);
+    const int r = (int)(i % ((int64_t)H * Dv));
+    const int h = r / Dv, j = r % Dv;
+    float v = rb_to_float<T>(a[(t * H + h) * Dc + j]);
+    if (gate != nullptr) v *= 1.0f / (1.0f + expf(-rb_to_float<T>(gate[t * ldg + h])));
+    out[i] = rb_from_float<T>(v);
+  }
+}
+
+RB_EXPORT int rb_head_gate(void* out, const void* a, const void* gate, int64_t ldg, int dtype, int T, int H, int Dv, int Dc,
+                           cudaStream_t stream) {
+  if (T == 0) return 0;
+  const int64_t n = (int64_t)T * H * Dv;
+  const int threads = 256;
+  const int64_t most = (int64_t)rb_sm_count() * 16;
+  const int blocks = (int)((n + threads - 1) / threads < most ? (n + threads - 1) / threads : most);
+  if (dtype == RB_F32)
+    RB_LAUNCH("head_gate_kernel", (head_gate_kernel<float>), blocks, threads, 0, stream, (float*)out, (const float*)a, (const float*)gate, ldg, n, H, Dv, Dc);
+  else if (dtype == RB_BF16)
+    RB_LAUNCH("head_gate_kernel", (head_gate_kernel<__nv_bfloat16>), blocks, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)a, (const __nv_bfloat16*)gate, ldg, n, H, Dv, Dc);
+  else
+    RB_FAIL("rb_head_gate: unknown dtype %d", dtype);
+  RB_CHECK_LAUNCH("rb_head_gate");
+  return 0;
+}
+
+// ---------------------------------------------------------------- gated activation with a limit
+// out = g' * sigmoid(alpha * g') * (u' + shift),  g' = min(g, limit),  u' = clamp(u, -limit, limit)
+// (limit <= 0: no limit).  alpha = 1, shift = 0 without a limit is SiLU(gate) * up.  Row layouts as rb_silu_mul.
+template <typename T, typename TI>
+__global__ void gated_act_kernel(T* __restrict__ out, const TI* __restrict__ gu, int64_t n, int F, int64_t ld, int block,
+                                 float alpha, float limit, float shift) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / F;
+    const int j = (int)(i % F);
+    const int64_t at_g = block > 0 ? (int64_t)(j / block) * 2 * block + j % block : j;
+    const int64_t at_u = block > 0 ? at_g + block : (int64_t)F + j;
+    float g = rb_to_float<TI>(gu[t * ld + at_g]);
+    float u = rb_to_float<TI>(gu[t * ld + at_u]);
+    if (limit > 0.f) {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+    }
+    out[i] = rb_from_float<T>(g / (1.0f + expf(-alpha * g)) * (u + shift));
+  }
+}
+
+RB_EXPORT int rb_gated_act(void* out, const void* gate_up, int dtype, int in_dtype, int T, int F, int64_t ld, int block,
+                           float alpha, float limit, float shift, cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(block >= 0 && (block == 0 ? ld >= 2 * (int64_t)F : ld >= ((int64_t)(F + block - 1) / block) * 2 * block),
+             "rb_gated_act: rows of %lld values do not hold %d features in blocks of %d", (long long)ld, F, block);
+  const int64_t n = (int64_t)T * F;
+  const int threads = 256;
+  const int64_t most = (int64_t)rb_sm_count() * 16;
+  const int blocks = (int)((n + threads - 1) / threads < most ? (n + threads - 1) / threads : most);
+  if (dtype == RB_F32 && in_dtype == RB_F32)
+    RB_LAUNCH("gated_act_kernel", (gated_act_kernel<float, float>), blocks, threads, 0, stream, (float*)out, (const float*)gate_up, n, F, ld, block, alpha, limit, shift);
+  else if (dtype == RB_BF16 && in_dtype == RB_BF16)
+    RB_LAUNCH("gated_act_kernel", (gated_act_kernel<__nv_bfloat16, __nv_bfloat16>), blocks, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, n, F, ld, block, alpha, limit, shift);
+  else if (dtype == RB_BF16 && in_dtype == RB_F32)
+    RB_LAUNCH("gated_act_kernel", (gated_act_kernel<__nv_bfloat16, float>), blocks, threads, 0, stream, (__nv_bfloat16*)out, (const float*)gate_up, n, F, ld, block, alpha, limit, shift);
+  else
+    RB_FAIL("rb_gated_act: unsupported dtypes %d <- %d", dtype, in_dtype);
+  RB_CHECK_LAUNCH("rb_gated_act");
+  return 0;
+}
+
 RB_CHECK_READER(elementwise)

@@ -17,9 +17,14 @@ template <typename TA, typename TC>
 __global__ void __launch_bounds__(256) gemm_simple_kernel(TC* __restrict__ C, int64_t ldc,
                                                          const TA* __restrict__ A, int64_t lda,
                                                          const TA* __restrict__ W, int64_t ldw, int M, int N,
-                                                         int K, int accumulate, float alpha) {
+                                                         int K, int accumulate, float alpha, int64_t batch_c,
+                                                         int64_t batch_a, int64_t batch_w) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
+  // blockIdx.z: one of several independent products of equal sizes, their operands a fixed distance apart
+  C += blockIdx.z * batch_c;
+  A += blockIdx.z * batch_a;
+  W += blockIdx.z * batch_w;
   __shared__ float As[BK][BM + 1];
   __shared__ float Ws[BK][BN + 1];
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -73,16 +78,19 @@ __global__ void __launch_bounds__(256) gemm_simple_kernel(TC* __restrict__ C, in
 
 // a_dtype: dtype of A and W; c_dtype: dtype of C.  accumulate: C += instead of C =.
 // alpha multiplies the finished sum (1.0 leaves it as it is).
-RB_EXPORT int rb_gemm_simple(void* C, int64_t ldc, int c_dtype, const void* A, int64_t lda, const void* W,
-                             int64_t ldw, int a_dtype, int M, int N, int K, int accumulate,
-                             float alpha, cudaStream_t stream) {
-  if (M == 0 || N == 0) return 0;
+// n_batch products at once: product z reads A + z*batch_a and W + z*batch_w and writes C + z*batch_c
+// (distances in elements); block-diagonal matrices are the use.
+RB_EXPORT int rb_gemm_simple_batched(void* C, int64_t ldc, int c_dtype, const void* A, int64_t lda, const void* W,
+                                     int64_t ldw, int a_dtype, int M, int N, int K, int accumulate, float alpha,
+                                     int n_batch, int64_t batch_c, int64_t batch_a, int64_t batch_w,
+                                     cudaStream_t stream) {
+  if (M == 0 || N == 0 || n_batch == 0) return 0;
   RB_REQUIRE(M > 0 && N > 0 && K > 0, "rb_gemm_simple: bad sizes M=%d N=%d K=%d", M, N, K);
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  RB_REQUIRE(grid.y <= 65535, "rb_gemm_simple: M=%d too large for one launch", M);
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, n_batch);
+  RB_REQUIRE(grid.y <= 65535 && n_batch >= 1 && n_batch <= 65535, "rb_gemm_simple: M=%d, %d products: too large for one launch", M, n_batch);
 #define LAUNCH(TA, TC)                                                                                     \
   RB_LAUNCH("gemm_simple_kernel", (gemm_simple_kernel<TA, TC>), grid, 256, 0, stream, (TC*)C, ldc, (const TA*)A, \
-            lda, (const TA*)W, ldw, M, N, K, accumulate, alpha)
+            lda, (const TA*)W, ldw, M, N, K, accumulate, alpha, batch_c, batch_a, batch_w)
   if (a_dtype == RB_F32 && c_dtype == RB_F32) LAUNCH(float, float);
   else if (a_dtype == RB_BF16 && c_dtype == RB_F32) LAUNCH(__nv_bfloat16, float);
   else if (a_dtype == RB_BF16 && c_dtype == RB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -90,4 +98,10 @@ RB_EXPORT int rb_gemm_simple(void* C, int64_t ldc, int c_dtype, const void* A, i
 #undef LAUNCH
   RB_CHECK_LAUNCH("rb_gemm_simple");
   return 0;
+}
+
+RB_EXPORT int rb_gemm_simple(void* C, int64_t ldc, int c_dtype, const void* A, int64_t lda, const void* W,
+                             int64_t ldw, int a_dtype, int M, int N, int K, int accumulate,
+                             float alpha, cudaStream_t stream) {
+  return rb_gemm_simple_batched(C, ldc, c_dtype, A, lda, W, ldw, a_dtype, M, N, K, accumulate, alpha, 1, 0, 0, 0, stream);
 }

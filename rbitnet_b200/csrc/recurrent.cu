@@ -1,0 +1,318 @@
+// Recurrent mixers: what runs from token to token of a sequence, with the state kept per cache slot.
+//
+//   causal convolution  u_t[c] = b[c] + sum_j taps[c][j] * x_(t-(K-1-j))[c]      (K taps, the last is the current token's)
+//   gated linear unit   r = sigmoid(g_r), i = sigmoid(g_i), a = exp(-c * r * softplus(lam)),
+//                       S_t = a S_(t-1) + sqrt(1 - a^2) * i * u_t ;   out = S_t * gelu_tanh(y_t)
+//   matrix memory       m_t = max(f + m_(t-1), i);  C_t = e^(f + m_(t-1) - m_t) C_(t-1) + e^(i - m_t) k v^T;
+//                       n_t likewise with k alone;  o = C_t^T q / (max(|n_t . q|, e^(-m_t)) + floor)
+//
+// A step brings, per sequence, a run of consecutive rows (its next tokens); seq_first / seq_count
+// name each run, and the state of the run's slot is read at its start and written back at its end,
+// so a prompt may arrive whole, in portions or token by token.  States, gates, decays, exponentials
+// and sums are float32 whatever the dtype of the projections.
+#include "rb_common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float softplusf_(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
+__device__ __forceinline__ float gelu_tanh_(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// ---------------------------------------------------------------- causal convolution
+// x: rows [T, ldx] of the projections' dtype, the convolved channels at column x_off; the bias x_bias
+// is added to every input before the taps.  tail: [n_slots, K-1, C] float32, the last K-1 inputs
+// (with their bias) of the slot's sequence before this step; zeros at the start of a sequence.
+// tok_first: row of the first token of the row's run (null: every row is its own run).
+template <typename TI>
+__global__ void conv_causal_kernel(float* __restrict__ u, const TI* __restrict__ x, int64_t ldx, int x_off,
+                                   const float* __restrict__ x_bias, const float* __restrict__ taps,
+                                   const float* __restrict__ conv_bias, const float* __restrict__ tail,
+                                   const int* __restrict__ tok_first, const int* __restrict__ tok_slot, int C, int K) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  const int t = blockIdx.x;
+  const int first = tok_first != nullptr ? tok_first[t] : t;
+  const int slot = tok_slot[t];
+  const int j = t - first;                      // rows of this run before this one
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    float acc = conv_bias != nullptr ? conv_bias[c] : 0.f;
+    const float xb = x_bias != nullptr ? x_bias[c] : 0.f;
+    for (int d = 0; d < K; ++d) {               // d tokens back
+      float v;
+      if (d <= j) v = rb_to_float<TI>(x[(int64_t)(t - d) * ldx + x_off + c]) + xb;
+      else v = tail[((int64_t)slot * (K - 1) + (K - 1 + j - d)) * C + c];
+      acc = fmaf(taps[(int64_t)c * K + (K - 1 - d)], v, acc);
+    }
+    u[(int64_t)t * C + c] = acc;
+  }
+}
+
+// ---------------------------------------------------------------- gated linear recurrent unit
+// One thread per (run, channel).  gates: [T, blocks, 2, Wb] float32 pre-activations (recurrence gate,
+// input gate) of the channel's block.  Also moves the convolution's tail on to the end of the run.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(64) gated_scan_kernel(
+    TO* __restrict__ out, const float* __restrict__ u, const float* __restrict__ gates, const float* __restrict__ gate_r_bias,
+    const float* __restrict__ gate_i_bias, const float* __restrict__ lam, float decay_scale, const TI* __restrict__ xy,
+    int64_t ldxy, int x_off, int y_off, const float* __restrict__ x_bias, const float* __restrict__ y_bias,
+    float* __restrict__ state, float* __restrict__ tail, const int* __restrict__ seq_first,
+    const int* __restrict__ seq_count, const int* __restrict__ tok_slot, int W, int Wb, int K) {
+  rb_pdl_launch_dependents();
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= W) return;
+  const float sp = decay_scale * softplusf_(lam[c]);
+  const float br = gate_r_bias[c], bi = gate_i_bias[c];
+  const float yb = y_bias != nullptr ? y_bias[c] : 0.f;
+  const float xb = x_bias != nullptr ? x_bias[c] : 0.f;
+  const int blk = c / Wb, o = c % Wb;
+  rb_pdl_wait();
+  const int first = seq_first != nullptr ? seq_first[blockIdx.x] : blockIdx.x;
+  const int n = seq_count != nullptr ? seq_count[blockIdx.x] : 1;
+  const int slot = tok_slot[first];
+  float S = state[(int64_t)slot * W + c];
+  for (int t = first; t < first + n; ++t) {
+    const float* g = gates + ((int64_t)t * (W / Wb) + blk) * 2 * Wb;
+    const float r = sigmoidf_(g[o] + br);
+    const float i = sigmoidf_(g[Wb + o] + bi);
+    const float a = expf(-sp * r);
+    S = fmaf(a, S, sqrtf(1.0f - a * a) * i * u[(int64_t)t * W + c]);
+    const float y = gelu_tanh_(rb_to_float<TI>(xy[(int64_t)t * ldxy + y_off + c]) + yb);
+    out[(int64_t)t * W + c] = rb_from_float<TO>(S * y);
+  }
+  state[(int64_t)slot * W + c] = S;
+  // the last K-1 inputs of the sequence, oldest first
+  float keep[8];
+  for (int k = 0; k < K - 1; ++k) {
+    const int back = K - 2 - k;                 // tokens before the run's last one
+    keep[k] = back < n ? rb_to_float<TI>(xy[(int64_t)(first + n - 1 - back) * ldxy + x_off + c]) + xb
+                       : tail[((int64_t)slot * (K - 1) + (k + n)) * W + c];
+  }
+  for (int k = 0; k < K - 1; ++k) tail[((int64_t)slot * (K - 1) + k) * W + c] = keep[k];
+}
+
+// ---------------------------------------------------------------- matrix memory
+// One block per (run, head, tile of value columns).  A thread owns one value column j and every P-th
+// row d of the memory (R rows at most), so a token costs it 2 R multiply-adds and the sums over d are
+// finished with log2(P) shuffles.  Rows of the projections: [q (H D) | k (H D) | v (H Dv) | ... ], gate
+// pre-activations at columns i_off + h and f_off + h.  Tokens are staged TT at a time in shared memory.
+constexpr int MM_THREADS = 128;
+constexpr int MM_TT = 16;
+
+template <typename TI, int R>
+__global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(
+    float* __restrict__ o_out, const TI* __restrict__ proj, int64_t ld, int q_off, int k_off, int v_off, int i_off,
+    int f_off, const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap, float q_scale,
+    float floor_add, float* __restrict__ C_state, float* __restrict__ n_state, float* __restrict__ m_state,
+    const int* __restrict__ seq_first, const int* __restrict__ seq_count, const int* __restrict__ tok_slot, int H, int D,
+    int Dv, int P) {
+  rb_pdl_launch_dependents();
+  extern __shared__ __align__(16) float sm[];
+  const int cols = MM_THREADS / P;
+  float* s_q = sm;                       // [TT][D]
+  float* s_k = s_q + MM_TT * D;          // [TT][D]
+  float* s_v = s_k + MM_TT * D;          // [TT][cols]
+  float* s_i = s_v + MM_TT * cols;       // [TT]
+  float* s_f = s_i + MM_TT;              // [TT]
+  const int h = blockIdx.y;
+  const int col = threadIdx.x / P, part = threadIdx.x % P;
+  const int j = blockIdx.z * cols + col;
+  const bool live = j < Dv;
+  const float ib = i_bias != nullptr ? i_bias[h] : 0.f, fb = f_bias != nullptr ? f_bias[h] : 0.f;
+  rb_pdl_wait();
+  const int first = seq_first != nullptr ? seq_first[blockIdx.x] : blockIdx.x;
+  const int n = seq_count != nullptr ? seq_count[blockIdx.x] : 1;
+  const int slot = tok_slot[first];
+  float Cr[R], nr[R];
+  float* Cs = C_state + ((int64_t)slot * H + h) * D * Dv;
+  float* ns = n_state + ((int64_t)slot * H + h) * D;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int d = part + P * r;
+    Cr[r] = (live && d < D) ? Cs[(int64_t)d * Dv + j] : 0.f;
+    nr[r] = d < D ? ns[d] : 0.f;
+  }
+  float m = m_state[(int64_t)slot * H + h];
+  for (int t0 = 0; t0 < n; t0 += MM_TT) {
+    const int nt = min(MM_TT, n - t0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < nt * D; e += MM_THREADS) {
+      const int tt = e / D, d = e % D;
+      const TI* row = proj + (int64_t)(first + t0 + tt) * ld;
+      s_q[tt * D + d] = rb_to_float<TI>(row[q_off + h * D + d]) * q_scale;
+      s_k[tt * D + d] = rb_to_float<TI>(row[k_off + h * D + d]);
+    }
+    for (int e = threadIdx.x; e < nt * cols; e += MM_THREADS) {
+      const int tt = e / cols, cc = e % cols;
+      const int jj = blockIdx.z * cols + cc;
+      s_v[tt * cols + cc] = jj < Dv ? rb_to_float<TI>(proj[(int64_t)(first + t0 + tt) * ld + v_off + h * Dv + jj]) : 0.f;
+    }
+    for (int tt = threadIdx.x; tt < nt; tt += MM_THREADS) {
+      const TI* row = proj + (int64_t)(first + t0 + tt) * ld;
+      const float ip = rb_to_float<TI>(row[i_off + h]) + ib, fp = rb_to_float<TI>(row[f_off + h]) + fb;
+      const float fc = cap * tanhf(fp / cap);
+      s_i[tt] = cap * tanhf(ip / cap);
+      s_f[tt] = fminf(fc, 0.f) - log1pf(expf(-fabsf(fc)));       // log sigmoid
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float ig = s_i[tt], fg = s_f[tt];
+      const float m_new = fmaxf(fg + m, ig);
+      const float keep = expf(fg + m - m_new), take = expf(ig - m_new);
+      m = m_new;
+      const float tv = take * s_v[tt * cols + col];
+      float num = 0.f, nq = 0.f;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int d = part + P * r;
+        if (d < D) {
+          const float kd = s_k[tt * D + d], qd = s_q[tt * D + d];
+          Cr[r] = fmaf(keep, Cr[r], tv * kd);
+          nr[r] = fmaf(keep, nr[r], take * kd);
+          num = fmaf(Cr[r], qd, num);
+          nq = fmaf(nr[r], qd, nq);
+        }
+      }
+      for (int off = P >> 1; off > 0; off >>= 1) {
+        num += __shfl_xor_sync(0xffffffffu, num, off);
+        nq += __shfl_xor_sync(0xffffffffu, nq, off);
+      }
+      if (live && part == 0) {
+        const float den = fmaxf(fabsf(nq), expf(-m)) + floor_add;
+        o_out[(int64_t)(first + t0 + tt) * H * Dv + h * Dv + j] = num / den;
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int d = part + P * r;
+    if (live && d < D) Cs[(int64_t)d * Dv + j] = Cr[r];
+    if (blockIdx.z == 0 && col == 0 && d < D) ns[d] = nr[r];
+  }
+  if (blockIdx.z == 0 && threadIdx.x == 0) m_state[(int64_t)slot * H + h] = m;
+}
+
+// Per (token, head): o / rms(o) over the head's Dv values, times the weight, times sigmoid(gate).
+// One warp each.  gate: the projections' rows, at column g_off.
+template <typename TI, typename TO>
+__global__ void head_norm_gate_kernel(TO* __restrict__ out, const float* __restrict__ o, const float* __restrict__ w,
+                                      const TI* __restrict__ proj, int64_t ld, int g_off, int n_rows, int H, int Dv,
+                                      float eps) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (int64_t)n_rows * H) return;
+  const int t = (int)(item / H), h = (int)(item % H);
+  const float* row = o + ((int64_t)t * H + h) * Dv;
+  float ss = 0.f;
+  for (int j = lane; j < Dv; j += 32) ss += row[j] * row[j];
+  ss = rb_warp_sum(ss);
+  const float r = 1.0f / sqrtf(ss / (float)Dv + eps);
+  for (int j = lane; j < Dv; j += 32) {
+    const float g = rb_to_float<TI>(proj[(int64_t)t * ld + g_off + h * Dv + j]);
+    out[((int64_t)t * H + h) * Dv + j] = rb_from_float<TO>(row[j] * r * w[h * Dv + j] * sigmoidf_(g));
+  }
+}
+
+}  // namespace
+
+RB_EXPORT int rb_conv_causal(float* u, const void* x, int64_t ldx, int x_off, int x_dtype, const float* x_bias,
+                             const float* taps, const float* conv_bias, const float* tail, const int* tok_first,
+                             const int* tok_slot, int T, int C, int K, cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(C > 0 && K >= 1, "rb_conv_causal: bad sizes C=%d K=%d", C, K);
+  const int threads = 128;
+  int by = (C + threads - 1) / threads;
+  if (by > 64) by = 64;
+  const dim3 grid(T, by);
+  if (x_dtype == RB_F32)
+    RB_LAUNCH("conv_causal_kernel", (conv_causal_kernel<float>), grid, threads, 0, stream, u, (const float*)x, ldx, x_off, x_bias, taps, conv_bias, tail, tok_first, tok_slot, C, K);
+  else if (x_dtype == RB_BF16)
+    RB_LAUNCH("conv_causal_kernel", (conv_causal_kernel<__nv_bfloat16>), grid, threads, 0, stream, u, (const __nv_bfloat16*)x, ldx, x_off, x_bias, taps, conv_bias, tail, tok_first, tok_slot, C, K);
+  else
+    RB_FAIL("rb_conv_causal: unknown dtype %d", x_dtype);
+  RB_CHECK_LAUNCH("rb_conv_causal");
+  return 0;
+}
+
+RB_EXPORT int rb_gated_scan(void* out, int out_dtype, const float* u, const float* gates, const float* gate_r_bias,
+                            const float* gate_i_bias, const float* lam, float decay_scale, const void* xy, int64_t ldxy,
+                            int xy_dtype, int x_off, int y_off, const float* x_bias, const float* y_bias, float* state,
+                            float* tail, const int* seq_first, const int* seq_count, const int* tok_slot, int n_seq, int W,
+                            int Wb, int K, cudaStream_t stream) {
+  if (n_seq == 0) return 0;
+  RB_REQUIRE(W > 0 && Wb > 0 && W % Wb == 0, "rb_gated_scan: width %d is not made of blocks of %d", W, Wb);
+  RB_REQUIRE(K >= 1 && K <= 9, "rb_gated_scan: %d taps (1..9 are built)", K);
+  const dim3 grid(n_seq, (W + 63) / 64);
+#define LAUNCH(TI, TO)                                                                                              \
+  RB_LAUNCH("gated_scan_kernel", (gated_scan_kernel<TI, TO>), grid, 64, 0, stream, (TO*)out, u, gates, gate_r_bias,  \
+            gate_i_bias, lam, decay_scale, (const TI*)xy, ldxy, x_off, y_off, x_bias, y_bias, state, tail, seq_first, \
+            seq_count, tok_slot, W, Wb, K)
+  if (xy_dtype == RB_F32 && out_dtype == RB_F32) LAUNCH(float, float);
+  else if (xy_dtype == RB_F32 && out_dtype == RB_BF16) LAUNCH(float, __nv_bfloat16);
+  else if (xy_dtype == RB_BF16 && out_dtype == RB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else RB_FAIL("rb_gated_scan: unsupported dtypes %d -> %d", xy_dtype, out_dtype);
+#undef LAUNCH
+  RB_CHECK_LAUNCH("rb_gated_scan");
+  return 0;
+}
+
+// Lanes per value column for a memory of D rows: the smallest power of two that leaves a thread at most 32 rows.
+RB_EXPORT int rb_matrix_memory_lanes(int D) {
+  int P = 1;
+  while ((D + P - 1) / P > 32 && P < 32) P *= 2;
+  return P;
+}
+
+RB_EXPORT int rb_matrix_memory(float* o_out, const void* proj, int64_t ld, int proj_dtype, int q_off, int k_off, int v_off,
+                               int i_off, int f_off, const float* i_bias, const float* f_bias, float cap, float q_scale,
+                               float floor_add, float* C_state, float* n_state, float* m_state, const int* seq_first,
+                               const int* seq_count, const int* tok_slot, int n_seq, int H, int D, int Dv,
+                               cudaStream_t stream) {
+  if (n_seq == 0) return 0;
+  RB_REQUIRE(H > 0 && D > 0 && Dv > 0 && D <= 1024, "rb_matrix_memory: bad sizes H=%d D=%d Dv=%d (D up to 1024)", H, D, Dv);
+  RB_REQUIRE(cap > 0.f, "rb_matrix_memory: the gates' cap must be positive");
+  const int P = rb_matrix_memory_lanes(D);
+  const int per = (D + P - 1) / P;
+  const int cols = MM_THREADS / P;
+  const dim3 grid(n_seq, H, (Dv + cols - 1) / cols);
+  RB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "rb_matrix_memory: grid %d x %d", grid.y, grid.z);
+  const size_t smem = (size_t)(MM_TT * (2 * D + cols + 2)) * sizeof(float);
+#define LAUNCH(TI, RR)                                                                                              \
+  do {                                                                                                              \
+    if (smem > 48 * 1024)                                                                                           \
+      RB_CUDA(cudaFuncSetAttribute(matrix_memory_kernel<TI, RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    RB_LAUNCH("matrix_memory_kernel", (matrix_memory_kernel<TI, RR>), grid, MM_THREADS, smem, stream, o_out,        \
+              (const TI*)proj, ld, q_off, k_off, v_off, i_off, f_off, i_bias, f_bias, cap, q_scale, floor_add,      \
+              C_state, n_state, m_state, seq_first, seq_count, tok_slot, H, D, Dv, P);                              \
+  } while (0)
+  if (proj_dtype == RB_F32) {
+    if (per <= 16) LAUNCH(float, 16); else LAUNCH(float, 32);
+  } else if (proj_dtype == RB_BF16) {
+    if (per <= 16) LAUNCH(__nv_bfloat16, 16); else LAUNCH(__nv_bfloat16, 32);
+  } else {
+    RB_FAIL("rb_matrix_memory: unknown dtype %d", proj_dtype);
+  }
+#undef LAUNCH
+  RB_CHECK_LAUNCH("rb_matrix_memory");
+  return 0;
+}
+
+RB_EXPORT int rb_head_norm_gate(void* out, int out_dtype, const float* o, const float* w, const void* proj, int64_t ld,
+                                int proj_dtype, int g_off, int T, int H, int Dv, float eps, cudaStream_t stream) {
+  if (T == 0) return 0;
+  const int64_t items = (int64_t)T * H;
+  const int blocks = (int)((items + 3) / 4);
+#define LAUNCH(TI, TO)                                                                                              \
+  RB_LAUNCH("head_norm_gate_kernel", (head_norm_gate_kernel<TI, TO>), blocks, 128, 0, stream, (TO*)out, o, w,        \
+            (const TI*)proj, ld, g_off, T, H, Dv, eps)
+  if (proj_dtype == RB_F32 && out_dtype == RB_F32) LAUNCH(float, float);
+  else if (proj_dtype == RB_F32 && out_dtype == RB_BF16) LAUNCH(float, __nv_bfloat16);
+  else if (proj_dtype == RB_BF16 && out_dtype == RB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else RB_FAIL("rb_head_norm_gate: unsupported dtypes %d -> %d", proj_dtype, out_dtype);
+#undef LAUNCH
+  RB_CHECK_LAUNCH("rb_head_norm_gate");
+  return 0;
+}

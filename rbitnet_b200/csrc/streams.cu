@@ -1,0 +1,194 @@
+// Several residual streams per token (hyper-connections) and the glue between two sublayers.
+//
+// The residual state of a token is s rows X[t][0..s-1][0..E-1] (float32).  A sublayer reads the
+// mix u = sum_k in[k] X_k through an RMS norm, and its result y is written back to all streams at
+// once from the old ones:  X'_j = sum_k mix[k][j] X_k + out[j] * y.   With s = 1, in = out = mix = 1
+// this is the ordinary residual sum.
+//
+// One kernel does everything that lies between the products of two sublayers, one block per token:
+//   1. y: the sublayer's result, or the mean of up to MAX_Y results each under its own RMS norm
+//      (mixers that run side by side);
+//   2. the write into the streams (skipped without y);
+//   3. the next sublayer's read and its norm (skipped without a next sublayer).
+// Every part can also run alone, which is how the fused call is tested against its pieces.
+// All arithmetic is float32.
+#include "rb_common.cuh"
+
+namespace {
+
+constexpr int MAX_STREAMS = 8;
+constexpr int MAX_Y = 4;
+
+struct StreamStepArgs {
+  float* X;                      // [T, s, E]; null: only the results are combined (into y_out)
+  int s, E;
+  const float* y[MAX_Y];         // [T, E] each; n_y == 0: nothing is written
+  const float* y_norm[MAX_Y];    // [E] each, or null: y[0] is taken as it is
+  int n_y;
+  const float* mix;              // [s, s], indexed [from, to]
+  const float* w_out;            // [s]
+  const float* w_in;             // [s] of the NEXT read, or null
+  const float* norm_w;           // [E] of the next read's norm
+  float eps;
+  void* h_out;                   // [T, E] in the compute dtype
+  float* y_out;                  // optional [T, E]: the combined y, for whoever wants it alone
+};
+
+template <typename TO>
+__global__ void __launch_bounds__(256) stream_step_kernel(StreamStepArgs a) {
+  rb_pdl_launch_dependents();
+  __shared__ float scratch[33];
+  __shared__ float s_mix[MAX_STREAMS * MAX_STREAMS], s_out[MAX_STREAMS], s_in[MAX_STREAMS];
+  extern __shared__ __align__(16) float urow[];     // E floats: the next read's mix
+  const int t = blockIdx.x, s = a.s, E = a.E;
+  // the small tables are weights: they do not depend on the kernel before
+  if (threadIdx.x < s * s && a.n_y > 0 && a.mix != nullptr) s_mix[threadIdx.x] = a.mix[threadIdx.x];
+  if (threadIdx.x < s) {
+    s_out[threadIdx.x] = (a.n_y > 0 && a.w_out != nullptr) ? a.w_out[threadIdx.x] : 0.f;
+    s_in[threadIdx.x] = a.w_in != nullptr ? a.w_in[threadIdx.x] : 0.f;
+  }
+  rb_pdl_wait();
+  // 1. factors of the results' norms
+  float yfac[MAX_Y];
+  const bool normed = a.n_y > 0 && a.y_norm[0] != nullptr;
+#pragma unroll
+  for (int k = 0; k < MAX_Y; ++k) {
+    yfac[k] = 1.f;
+    if (normed && k < a.n_y) {
+      const float* yr = a.y[k] + (int64_t)t * E;
+      float ss = 0.f;
+      for (int e = threadIdx.x; e < E; e += blockDim.x) ss += yr[e] * yr[e];
+      ss = rb_block_sum(ss, scratch);
+      yfac[k] = 1.0f / sqrtf(ss / (float)E + a.eps);
+    }
+  }
+  __syncthreads();
+  float* Xt = a.X + (int64_t)t * s * E;
+  float ss = 0.f;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    float xs[MAX_STREAMS];
+#pragma unroll
+    for (int k = 0; k < MAX_STREAMS; ++k) xs[k] = (k < s && a.X != nullptr) ? Xt[(int64_t)k * E + e] : 0.f;
+    if (a.n_y > 0) {
+      float y;
+      if (normed) {
+        y = 0.f;
+#pragma unroll
+        for (int k = 0; k < MAX_Y; ++k)
+          if (k < a.n_y) y += a.y[k][(int64_t)t * E + e] * yfac[k] * a.y_norm[k][e];
+        y *= 1.0f / (float)a.n_y;
+      } else {
+        y = a.y[0][(int64_t)t * E + e];
+      }
+      if (a.y_out != nullptr) a.y_out[(int64_t)t * E + e] = y;
+      if (a.X == nullptr) continue;
+      float nx[MAX_STREAMS];
+#pragma unroll
+      for (int j = 0; j < MAX_STREAMS; ++j) {
+        if (j >= s) { nx[j] = 0.f; continue; }
+        float v = 0.f;
+#pragma unroll
+        for (int k = 0; k < MAX_STREAMS; ++k)
+          if (k < s) v = fmaf(s_mix[k * s + j], xs[k], v);
+        nx[j] = fmaf(s_out[j], y, v);
+      }
+#pragma unroll
+      for (int j = 0; j < MAX_STREAMS; ++j)
+        if (j < s) { xs[j] = nx[j]; Xt[(int64_t)j * E + e] = nx[j]; }
+    }
+    if (a.w_in != nullptr) {
+      float u = 0.f;
+#pragma unroll
+      for (int k = 0; k < MAX_STREAMS; ++k)
+        if (k < s) u = fmaf(s_in[k], xs[k], u);
+      urow[e] = u;
+      ss += u * u;
+    }
+  }
+  if (a.w_in == nullptr) return;
+  ss = rb_block_sum(ss, scratch);
+  const float r = 1.0f / sqrtf(ss / (float)E + a.eps);
+  TO* h = (TO*)a.h_out + (int64_t)t * E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) h[e] = rb_from_float<TO>(urow[e] * a.norm_w[e] * r);
+}
+
+// X[t][k][:] = x[t][:] for every stream k
+__global__ void streams_expand_kernel(float* __restrict__ X, const float* __restrict__ x, int s, int E) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  const int t = blockIdx.x;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const float v = x[(int64_t)t * E + e];
+    for (int k = 0; k < s; ++k) X[((int64_t)t * s + k) * E + e] = v;
+  }
+}
+
+// out[r][:] = sum_k X[r][k][:], streams added in ascending order
+__global__ void streams_sum_kernel(float* __restrict__ out, const float* __restrict__ X, int s, int E) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  const int t = blockIdx.x;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    float v = 0.f;
+    for (int k = 0; k < s; ++k) v += X[((int64_t)t * s + k) * E + e];
+    out[(int64_t)t * E + e] = v;
+  }
+}
+
+}  // namespace
+
+RB_EXPORT int rb_streams_max() { return MAX_STREAMS; }
+RB_EXPORT int rb_streams_max_results() { return MAX_Y; }
+
+// y: n_y pointers (host array) to [T, E] float32; y_norm: n_y pointers to [E] weights, or null for a
+// single result taken as it is.  w_in null: no next read.  n_y == 0: only the read.
+RB_EXPORT int rb_stream_step(float* X, int T, int s, int E, const float* const* y, const float* const* y_norm, int n_y,
+                             const float* mix, const float* w_out, const float* w_in, const float* norm_w, float eps,
+                             void* h_out, int h_dtype, float* y_out, cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(s >= 1 && s <= MAX_STREAMS, "rb_stream_step: %d streams (1..%d are built)", s, MAX_STREAMS);
+  RB_REQUIRE(n_y >= 0 && n_y <= MAX_Y, "rb_stream_step: %d results to combine (0..%d are built)", n_y, MAX_Y);
+  RB_REQUIRE(E > 0 && (size_t)E * 4 <= 200 * 1024, "rb_stream_step: width %d", E);
+  RB_REQUIRE(n_y == 0 || X == nullptr || (mix != nullptr && w_out != nullptr), "rb_stream_step: a write needs mix and out weights");
+  RB_REQUIRE(X != nullptr || (y_out != nullptr && w_in == nullptr && n_y > 0), "rb_stream_step: without a state only results are combined");
+  RB_REQUIRE(n_y <= 1 || y_norm != nullptr, "rb_stream_step: several results are combined under their norms");
+  RB_REQUIRE(w_in == nullptr || (norm_w != nullptr && h_out != nullptr), "rb_stream_step: a read needs its norm and an output");
+  StreamStepArgs a{};
+  a.X = X; a.s = s; a.E = E; a.n_y = n_y;
+  for (int k = 0; k < n_y; ++k) {
+    a.y[k] = y[k];
+    a.y_norm[k] = y_norm != nullptr ? y_norm[k] : nullptr;
+  }
+  a.mix = mix; a.w_out = w_out; a.w_in = w_in; a.norm_w = norm_w; a.eps = eps; a.h_out = h_out; a.y_out = y_out;
+  const size_t smem = w_in != nullptr ? (size_t)E * sizeof(float) : 0;
+  const int threads = E >= 1024 ? 256 : 128;
+  if (h_dtype == RB_BF16) {
+    if (smem > 48 * 1024)
+      RB_CUDA(cudaFuncSetAttribute(stream_step_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    RB_LAUNCH("stream_step_kernel", (stream_step_kernel<__nv_bfloat16>), T, threads, smem, stream, a);
+  } else if (h_dtype == RB_F32) {
+    if (smem > 48 * 1024)
+      RB_CUDA(cudaFuncSetAttribute(stream_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    RB_LAUNCH("stream_step_kernel", (stream_step_kernel<float>), T, threads, smem, stream, a);
+  } else {
+    RB_FAIL("rb_stream_step: unknown dtype %d", h_dtype);
+  }
+  RB_CHECK_LAUNCH("rb_stream_step");
+  return 0;
+}
+
+RB_EXPORT int rb_streams_expand(float* X, const float* x, int T, int s, int E, cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(s >= 1 && E > 0, "rb_streams_expand: bad sizes s=%d E=%d", s, E);
+  RB_LAUNCH("streams_expand_kernel", (streams_expand_kernel), T, 256, 0, stream, X, x, s, E);
+  RB_CHECK_LAUNCH("rb_streams_expand");
+  return 0;
+}
+
+RB_EXPORT int rb_streams_sum(float* out, const float* X, int T, int s, int E, cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(s >= 1 && E > 0, "rb_streams_sum: bad sizes s=%d E=%d", s, E);
+  RB_LAUNCH("streams_sum_kernel", (streams_sum_kernel), T, 256, 0, stream, out, X, s, E);
+  RB_CHECK_LAUNCH("rb_streams_sum");
+  return 0;
+}

@@ -31,6 +31,11 @@ class Model:
                 part.bind(weights, ops)
             self.blocks.append(block)
         self.embedding_scale, self.logit_scale = float(spec.embedding_scale), float(spec.logit_scale)
+        self.residual_streams = int(getattr(spec, "residual_streams", 1) or 1)
+        for i, block in enumerate(self.blocks):
+            if int(getattr(block, "streams", 1)) != self.residual_streams:
+                raise ValueError(f"layer {i} works on {getattr(block, 'streams', 1)} residual streams, the model has "
+                                 f"{self.residual_streams}")
         self.final_norm = build_part("norm", spec.final_norm)
         self.final_norm.bind({k: tensors[n].to(dev) for k, n in spec.final_norm_names.items()}, ops)
         self.embedding = ops.prepare_embedding(tensors[spec.embedding_name])
@@ -73,8 +78,8 @@ class Model:
                         raise ValueError(f"schedule entry {e} sees {need.window or 'all'} keys but reads the cache of "
                                          f"entry {entry.reads_cache_of}, which keeps only the last {theirs.window}")
             st = mixer.state_need()
-            if st is not None:
-                state_needs[e] = st
+            if st:
+                state_needs[e] = st            # one StateNeed, or several by name
         return cache_needs, reads, state_needs
 
     def weight_bytes(self) -> int:
@@ -97,11 +102,24 @@ class Model:
         """Runs the step's tokens; returns float32 logits [wanted rows, vocab] or None."""
         ops, meta = ctx.ops, ctx.meta
         x = ops.embed(meta.token_ids, self.embedding, self.embedding_scale)   # float32 residual stream [T, E]
+        s = self.residual_streams
+        if s > 1:
+            x = ops.streams_expand(x, s)                                      # [T, s * E]: every stream starts as the embedding
         schedule, pending = self.spec.schedule, None
+        taps = getattr(ctx, "layer_outputs", None)                            # a list: the residual sum after every run of a layer
         for e, entry in enumerate(schedule):
             block = self.blocks[entry.layer]
+            if getattr(block, "chains_reads", False):
+                # a block that can hand the normed read of the next block's first sublayer on (see parts/block.py)
+                after = self.blocks[schedule[e + 1].layer] if e + 1 < len(schedule) else None
+                next_read = after.first_read() if getattr(after, "chains_reads", False) and taps is None else None
+                pending = block.run(ctx, x, e, pending=pending, next_read=next_read)
+                if taps is not None:
+                    taps.append(ops.streams_sum(x, s) if s > 1 else x.clone())
+                continue
             if not getattr(block, "chains_norms", False):
                 block.run(ctx, x, e)
+                pending = None
                 continue
             # a block that can hand the rows of the next block's first norm on (see parts/block.py)
             after = self.blocks[schedule[e + 1].layer] if e + 1 < len(schedule) else None
@@ -110,5 +128,7 @@ class Model:
         if meta.n_want == 0:
             return None
         rows = x if meta.want_every_row else ops.gather_rows(x, meta.want_rows)
+        if s > 1:
+            rows = ops.streams_sum(rows, s)
         h = self.final_norm.forward(ctx, rows)
         return ops.linear(h, self.head, out_dtype=torch.float32, scale=self.logit_scale)

@@ -21,6 +21,20 @@ _SIGNATURES = {
     "rb_silu_mul": [P, P, I, I, I, I, L, I, P],
     "rb_gather_rows": [P, P, P, I, I, P],
     "rb_gemm_simple": [P, L, I, P, L, P, L, I, I, I, I, I, F, P],
+    "rb_gemm_simple_batched": [P, L, I, P, L, P, L, I, I, I, I, I, F, I, L, L, L, P],
+    "rb_stream_step": [P, I, I, I, P, P, I, P, P, P, P, F, P, I, P, P],
+    "rb_streams_expand": [P, P, I, I, I, P],
+    "rb_streams_sum": [P, P, I, I, I, P],
+    "rb_streams_max": [],
+    "rb_streams_max_results": [],
+    "rb_norm_rotate_append": [P, P, L, I, P, P, F, P, F, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P],
+    "rb_head_gate": [P, P, P, L, I, I, I, I, I, P],
+    "rb_gated_act": [P, P, I, I, I, I, L, I, F, F, F, P],
+    "rb_conv_causal": [P, P, L, I, I, P, P, P, P, P, P, I, I, I, P],
+    "rb_gated_scan": [P, I, P, P, P, P, P, F, P, L, I, I, I, P, P, P, P, P, P, P, I, I, I, I, P],
+    "rb_matrix_memory": [P, P, L, I, I, I, I, I, I, P, P, F, F, F, P, P, P, P, P, P, I, I, I, I, P],
+    "rb_matrix_memory_lanes": [I],
+    "rb_head_norm_gate": [P, I, P, P, P, L, I, I, I, I, I, F, P],
     "rb_attention_simple": [P, P, I, P, P, P, I, I, P, P, I, I, I, I, F, I, P],
     "rb_sample": [P, P, L, I, I, P, P, P, P],
     "rb_sample_chunks": [I],

@@ -118,6 +118,8 @@ class CudaOps:
         #: a decode step's norms between two products are folded into them (see ``NormedRows``)
         self.fold_norms = True
         self.fold_norms_up_to = 16
+        #: what lies between two sublayers of a block over several residual streams is one kernel
+        self.fuse_streams = True
         #: tensor-core products of more than 256 tokens may share a weight tile's inner dimension
         #: between teams of CTAs (needs the workspace; tiles are taken in turn without it)
         _give_gemm_workspace(self.lib, self.device)
@@ -283,8 +285,19 @@ class CudaOps:
                 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
                 and x.stride(1) == 1 and w.stride(1) == 1)
 
-    def gated_linear(self, x: torch.Tensor, weight: GateUpWeight) -> torch.Tensor:
-        """silu(x Wg^T) * (x Wu^T) -> [T, inner] in the compute dtype."""
+    def gated_linear(self, x: torch.Tensor, weight: GateUpWeight, act=None) -> torch.Tensor:
+        """silu(x Wg^T) * (x Wu^T) -> [T, inner] in the compute dtype.  ``act`` = (alpha, limit, shift):
+        g' sigmoid(alpha g') (u' + shift) with g' = min(g, limit), u' = clamp(u, -limit, limit) instead."""
+        if act is not None:
+            if isinstance(x, NormedRows):
+                x = self.normed(x)
+            T, rows = x.shape[0], weight.w.shape[0]
+            gu = self.linear(x, LinearWeight(weight.w, rows, weight.n_in), out_dtype=torch.float32)
+            out = torch.empty((T, weight.inner), dtype=self.dtype, device=self.device)
+            alpha, limit, shift = act
+            self.lib.call("rb_gated_act", _ptr(out), _ptr(gu), self.code, F32, T, weight.inner, gu.stride(0),
+                          weight.block, float(alpha), float(limit), float(shift), self._stream())
+            return out
         pending = x if isinstance(x, NormedRows) else None
         if pending is not None:
             if weight.block == 16 and self._takes_pending(pending, weight.w):
@@ -435,6 +448,161 @@ class CudaOps:
             dev = torch.from_numpy(np.asarray([tok0, ntok], dtype=np.int32)).to(self.device)
             meta.extra[key] = (dev[0], dev[1], len(tok0))
         return meta.extra[key]
+
+    # ------------------------------------------------------------------ several residual streams
+    def streams_expand(self, x: torch.Tensor, s: int) -> torch.Tensor:
+        """[T, E] -> [T, s * E]: every stream a copy of the row."""
+        T, E = x.shape
+        out = torch.empty((T, s * E), dtype=torch.float32, device=self.device)
+        self.lib.call("rb_streams_expand", _ptr(out), _ptr(x), T, s, E, self._stream())
+        return out
+
+    def streams_sum(self, x: torch.Tensor, s: int) -> torch.Tensor:
+        """[R, s * E] -> [R, E]: the streams added up."""
+        R, E = x.shape[0], x.shape[1] // s
+        out = torch.empty((R, E), dtype=torch.float32, device=self.device)
+        self.lib.call("rb_streams_sum", _ptr(out), _ptr(x), R, s, E, self._stream())
+        return out
+
+    def stream_step(self, x: torch.Tensor, s: int, results=None, result_norms=None, norm_eps: float = 0.0,
+                    write=None, read=None, want_result: bool = False):
+        """What lies between two sublayers over a residual state ``x`` [T, s * E] (float32), in one launch:
+
+        ``results`` (float32 [T, E] each) with ``write`` = (mix [s, s], w_out [s]): x_j <- sum_k mix[k, j] x_k +
+        w_out[j] * y, where y is the one result, or with ``result_norms`` (a weight [E] per result) the
+        mean of the results each under its RMS norm (eps ``norm_eps``);
+        ``read`` = (w_in [s], norm weight [E], eps): returns norm(sum_k w_in[k] x_k) in the compute dtype.
+        Either part may be left out.  ``want_result``: also returns y."""
+        import ctypes
+        self._check(x, torch.float32, "stream_step state")
+        T, E = x.shape[0], x.shape[1] // s
+        n_y = len(results) if results else 0
+        ys = (ctypes.c_void_p * max(n_y, 1))(*[r.data_ptr() for r in (results or [])])
+        for r in results or []:
+            self._check(r, torch.float32, "stream_step result")
+        yn = None
+        if result_norms:
+            yn = (ctypes.c_void_p * n_y)(*[w.data_ptr() for w in result_norms])
+        mix, w_out = write if write is not None else (None, None)
+        w_in, norm_w, eps = read if read is not None else (None, None, norm_eps)
+        if result_norms and read is not None and float(eps) != float(norm_eps):
+            raise KernelError("stream_step: the results' norms and the read's norm have different eps")
+        h = torch.empty((T, E), dtype=self.dtype, device=self.device) if read is not None else None
+        y_out = torch.empty((T, E), dtype=torch.float32, device=self.device) if want_result else None
+        self.lib.call("rb_stream_step", _ptr(x), T, s, E, ys, yn, n_y, _ptr(mix), _ptr(w_out), _ptr(w_in), _ptr(norm_w),
+                      float(eps if read is not None else norm_eps), _ptr(h), self.code, _ptr(y_out), self._stream())
+        return (h, y_out) if want_result else h
+
+    def normed_mean(self, results, weights, eps: float) -> torch.Tensor:
+        """float32 [T, E]: the mean of the results, each divided by its root mean square and multiplied by its weight."""
+        import ctypes
+        T, E = results[0].shape
+        n = len(results)
+        out = torch.empty((T, E), dtype=torch.float32, device=self.device)
+        ys = (ctypes.c_void_p * n)(*[r.data_ptr() for r in results])
+        yn = (ctypes.c_void_p * n)(*[w.data_ptr() for w in weights])
+        # the combining part of the stream step alone: no state
+        self.lib.call("rb_stream_step", c_void_p(0), T, 1, E, ys, yn, n, c_void_p(0), c_void_p(0), c_void_p(0),
+                      c_void_p(0), float(eps), c_void_p(0), self.code, _ptr(out), self._stream())
+        return out
+
+    # ------------------------------------------------------------------ attention with a projection norm, partial rotation, a gate
+    def cache_head_width(self, head_dim: int, value_dim: int) -> int:
+        """The width of the cache rows that hold keys of ``head_dim`` and values of ``value_dim`` (both padded
+        with zeros to it): the larger of the two, in bfloat16 rounded up to a multiple of 16 so that the
+        tensor-core attention kernels take it."""
+        w = max(int(head_dim), int(value_dim))
+        return -(-w // 16) * 16 if self.dtype == torch.bfloat16 else w
+
+    def norm_rotate_append(self, proj: torch.Tensor, table, meta, view, n_heads: int, head_dim: int, value_dim: int,
+                           q_norm_w, k_norm_w, eps: float) -> torch.Tensor:
+        """From rows [q | k | v | ...] of the projections: q and k under an RMS norm over the whole
+        projection (if weights are given), the first rot_dim values of every head turned by position, k and v
+        appended to the cache (rows ``view.head_dim`` wide, padded with zeros); returns q [T, H, view.head_dim]."""
+        self._check(proj, self.dtype, "norm_rotate_append projections")
+        T, Dc, Kh = proj.shape[0], view.head_dim, view.n_kv_heads
+        if table is None:
+            freq, magnitude, interleaved, rot_dim = None, 1.0, True, 0
+        else:
+            freq, magnitude, interleaved, rot_dim = table
+        q = torch.empty((T, n_heads, Dc), dtype=self.dtype, device=self.device)
+        self.lib.call("rb_norm_rotate_append", _ptr(q), _ptr(proj), proj.stride(0), self.code, _ptr(q_norm_w), _ptr(k_norm_w),
+                      float(eps), _ptr(freq), float(magnitude), _ptr(meta.tok_pos), _ptr(meta.tok_slot), _ptr(view.k),
+                      _ptr(view.v), _ptr(view.page_table), view.max_pages, view.page_size, T, n_heads, Kh, head_dim,
+                      value_dim, Dc, rot_dim, 1 if interleaved else 0, 1, self._stream())
+        return q
+
+    def head_gate(self, a: torch.Tensor, proj: torch.Tensor, gate_column, n_heads: int, value_dim: int,
+                  cache_width: int) -> torch.Tensor:
+        """[T, H * cache_width] -> [T, H * value_dim]: the padding dropped and head h multiplied by
+        sigmoid(proj[t, gate_column + h]) (no gate: ``gate_column`` None)."""
+        if gate_column is None and value_dim == cache_width:
+            return a
+        T = a.shape[0]
+        out = torch.empty((T, n_heads * value_dim), dtype=self.dtype, device=self.device)
+        gate = c_void_p(proj.data_ptr() + gate_column * proj.element_size()) if gate_column is not None else c_void_p(0)
+        self.lib.call("rb_head_gate", _ptr(out), _ptr(a), gate, proj.stride(0), self.code, T, n_heads, value_dim,
+                      cache_width, self._stream())
+        return out
+
+    # ------------------------------------------------------------------ recurrent mixers
+    def _runs(self, meta):
+        """The step's runs of consecutive rows, one per sequence (device int32: first row, count; per row: the
+        first row of its run); None for a step of one token per sequence, where every row is its own run."""
+        if meta.single_token:
+            return None, None, None, meta.n_tokens
+        key = "runs"
+        if key not in meta.extra:
+            import numpy as np
+            n, T = len(meta.seqs), meta.n_tokens
+            packed = np.empty(2 * n + T, dtype=np.int32)
+            for i, c in enumerate(meta.seqs):
+                packed[i], packed[n + i] = c.offset, c.n_new
+                packed[2 * n + c.offset:2 * n + c.offset + c.n_new] = c.offset
+            dev = torch.from_numpy(packed).to(self.device)
+            meta.extra[key] = (dev[:n], dev[n:2 * n], dev[2 * n:], n)
+        return meta.extra[key]
+
+    def gated_recurrence(self, proj: torch.Tensor, p, state, meta) -> torch.Tensor:
+        """The gated linear recurrence of ``parts.recurrent.GatedLinearRecurrence`` ``p`` on rows
+        [x channels | y channels] (float32): S_t * gelu_tanh(y_t) as [T, inner] in the compute dtype; the
+        sequences' state (``state["S"]``, ``state["tail"]``) moves on."""
+        self._check(proj, torch.float32, "gated_recurrence projections")
+        T, W, B, K = proj.shape[0], p.inner, p.blocks, p.taps
+        Wb = W // B
+        first, count, tok_first, n_seq = self._runs(meta)
+        f = p.f32
+        tail = state.get("tail")
+        u = torch.empty((T, W), dtype=torch.float32, device=self.device)
+        self.lib.call("rb_conv_causal", _ptr(u), _ptr(proj), proj.stride(0), 0, F32, _ptr(f["x.b"]), _ptr(f["conv"]),
+                      _ptr(f["conv.b"]), _ptr(tail), _ptr(tok_first), _ptr(meta.tok_slot), T, W, K, self._stream())
+        gates = torch.empty((T, B, 2 * Wb), dtype=torch.float32, device=self.device)
+        self.lib.call("rb_gemm_simple_batched", _ptr(gates), gates.stride(0), F32, _ptr(u), u.stride(0), _ptr(p.w_gates), Wb,
+                      F32, T, 2 * Wb, Wb, 0, 1.0, B, 2 * Wb, Wb, 2 * Wb * Wb, self._stream())
+        out = torch.empty((T, W), dtype=self.dtype, device=self.device)
+        self.lib.call("rb_gated_scan", _ptr(out), self.code, _ptr(u), _ptr(gates), _ptr(f["ra.b"]), _ptr(f["ri.b"]),
+                      _ptr(f["lam"]), float(p.decay_scale), _ptr(proj), proj.stride(0), F32, 0, W, _ptr(f["x.b"]),
+                      _ptr(f["y.b"]), _ptr(state["S"]), _ptr(tail), _ptr(first), _ptr(count), _ptr(meta.tok_slot), n_seq,
+                      W, Wb, K, self._stream())
+        return out
+
+    def matrix_memory(self, proj: torch.Tensor, p, state, meta) -> torch.Tensor:
+        """The matrix memory of ``parts.recurrent.MatrixMemory`` ``p`` on rows [q | k | v | g | i | f] (float32):
+        the heads' outputs under their norm, weight and gate as [T, H * value_dim] in the compute dtype; the
+        sequences' state (``state["C"]``, ``["n"]``, ``["m"]``) moves on."""
+        self._check(proj, torch.float32, "matrix_memory projections")
+        T, H, D, Dv = proj.shape[0], p.n_heads, p.head_dim, p.value_dim
+        first, count, _, n_seq = self._runs(meta)
+        at = p.offsets()
+        o = torch.empty((T, H * Dv), dtype=torch.float32, device=self.device)
+        self.lib.call("rb_matrix_memory", _ptr(o), _ptr(proj), proj.stride(0), F32, at["q"], at["k"], at["v"], at["i"],
+                      at["f"], _ptr(p.i_bias), _ptr(p.f_bias), float(p.gate_cap), float(D) ** -0.5, float(p.floor),
+                      _ptr(state["C"]), _ptr(state["n"]), _ptr(state["m"]), _ptr(first), _ptr(count), _ptr(meta.tok_slot),
+                      n_seq, H, D, Dv, self._stream())
+        out = torch.empty((T, H * Dv), dtype=self.dtype, device=self.device)
+        self.lib.call("rb_head_norm_gate", _ptr(out), self.code, _ptr(o), _ptr(p.norm_w), _ptr(proj), proj.stride(0), F32,
+                      at["g"], T, H, Dv, float(p.norm_eps), self._stream())
+        return out
 
     def gather_rows(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         R, E = rows.shape[0], x.shape[1]

@@ -1,2 +1,3 @@
 """Architectures.  Importing this package registers them."""
 from . import llama  # noqa: F401
+from . import safuvik  # noqa: F401

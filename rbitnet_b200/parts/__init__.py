@@ -1,13 +1,17 @@
 from .spec import PartSpec, BlockSpec, ScheduleEntry, ModelSpec
-from .base import Part, Norm, PositionEncoding, Mixer, FeedForward, CacheNeed, StateNeed
+from .base import Part, Norm, PositionEncoding, Mixer, FeedForward, Connection, CacheNeed, StateNeed
 from .registry import register_part, unregister_part, known_parts, build_part, build_block
 from .norm import RMSNorm
 from .position import RotaryEncoding, NoPositionEncoding
 from .attention import Attention
 from .feed_forward import GatedDense
-from .block import PreNormBlock
+from .block import PreNormBlock, StreamBlock
+from .recurrent import GatedLinearRecurrence, MatrixMemory
+from .parallel import ParallelMixers
+from .connection import ResidualConnection, HyperConnection
 
 __all__ = ["PartSpec", "BlockSpec", "ScheduleEntry", "ModelSpec", "Part", "Norm", "PositionEncoding",
            "Mixer", "FeedForward", "CacheNeed", "StateNeed", "register_part", "unregister_part",
            "known_parts", "build_part", "build_block", "RMSNorm", "RotaryEncoding", "NoPositionEncoding", "Attention",
-           "GatedDense", "PreNormBlock"]
+           "GatedDense", "PreNormBlock", "StreamBlock", "Connection", "GatedLinearRecurrence", "MatrixMemory",
+           "ParallelMixers", "ResidualConnection", "HyperConnection"]

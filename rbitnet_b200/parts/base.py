@@ -9,9 +9,12 @@ Roles:
   norm              forward(ctx, x[T,E] float32) -> h[T,E] in the compute dtype
   position          describes how positions enter a mixer (``rotary()``)
   mixer             forward(ctx, h, entry, accumulate_into) ; adds its result to the
-                    float32 residual stream; may need cache (``cache_need``) and
-                    fixed-size per-sequence state (``state_need``)
-  feed_forward      forward(ctx, h, accumulate_into)
+                    float32 residual stream, or returns it as float32 rows when
+                    ``accumulate_into`` is None; may need cache (``cache_need``) and
+                    fixed-size per-sequence state (``state_need``: one tensor, or
+                    several by name)
+  feed_forward      forward(ctx, h, accumulate_into), likewise
+  connection        how a sublayer's result enters the residual state (``weights()``)
 """
 from __future__ import annotations
 
@@ -81,18 +84,32 @@ class Mixer(Part):
     def cache_need(self) -> Optional[CacheNeed]:
         return None
 
-    def state_need(self) -> Optional[StateNeed]:
+    def state_need(self):
+        """None, one ``StateNeed``, or a dict name -> ``StateNeed`` for a mixer that keeps several
+        tensors per sequence (``ctx.state_view(entry)`` then gives a dict of the same names)."""
         return None
 
-    def forward(self, ctx, h: torch.Tensor, entry: int, accumulate_into: torch.Tensor) -> None:
+    def forward(self, ctx, h: torch.Tensor, entry: int, accumulate_into: Optional[torch.Tensor] = None):
         """h[T, E]: the normed input rows of this step's tokens.  ``entry`` is the
         index of this run in the schedule (``ctx.cache_view(entry)``,
-        ``ctx.state_view(entry)``).  The result is added to ``accumulate_into``."""
+        ``ctx.state_view(entry)``).  The result is added to ``accumulate_into``; a mixer that
+        can also stand beside another one returns it as float32 [T, E] when that is None."""
         raise NotImplementedError
 
 
 class FeedForward(Part):
     role = "feed_forward"
 
-    def forward(self, ctx, h: torch.Tensor, accumulate_into: torch.Tensor) -> None:
+    def forward(self, ctx, h: torch.Tensor, accumulate_into: Optional[torch.Tensor] = None):
+        raise NotImplementedError
+
+
+class Connection(Part):
+    """How a sublayer reads the residual state and how its result enters it.  ``streams`` rows per
+    token; ``weights()`` gives float32 device tensors ``w_in`` [s], ``w_out`` [s], ``mix`` [s, s]
+    (indexed [from, to])."""
+    role = "connection"
+    streams = 1
+
+    def weights(self):
         raise NotImplementedError

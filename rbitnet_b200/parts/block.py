@@ -74,4 +74,69 @@ class PreNormBlock:
         return request.result
 
 
+class StreamBlock:
+    """Sublayers over a residual state of s rows per token (``x`` is [T, s * E] float32): a mixer and,
+    if the layer has one, a feed-forward, each with a norm and a connection (see ``parts/connection.py``):
+
+        h = norm(read(X));  y = sublayer(h);  X <- write(X, y)
+
+    Parts: "mixer", "mixer_norm", "mixer_connection", and none or all of "feed_forward", "ffn_norm",
+    "ffn_connection".  What lies between the products of two sublayers (the mean of the normed results of
+    mixers that run side by side, the write, the next read and its norm) is one kernel where the
+    operations fuse it (``ops.fuse_streams``), else a kernel each; the read of the next block's first
+    sublayer is handed on like a pending norm (``chains_reads``)."""
+
+    chains_reads = True
+
+    def __init__(self, spec):
+        self.spec = spec
+        self._parts = build_parts(spec)
+        for n in ("mixer", "mixer_norm", "mixer_connection"):
+            if n not in self._parts:
+                raise ValueError(f"a multi_stream block needs the part {n!r}")
+        ffn = [n for n in ("feed_forward", "ffn_norm", "ffn_connection") if n in self._parts]
+        if len(ffn) not in (0, 3):
+            raise ValueError("a multi_stream block has a feed-forward with its norm and connection, or none of them")
+        self.sublayers = [(self._parts["mixer"], self._parts["mixer_norm"], self._parts["mixer_connection"], True)]
+        if ffn:
+            self.sublayers.append((self._parts["feed_forward"], self._parts["ffn_norm"], self._parts["ffn_connection"], False))
+        self.streams = self._parts["mixer_connection"].streams
+        if any(c.streams != self.streams for _, _, c, _ in self.sublayers):
+            raise ValueError("a multi_stream block's connections must have the same number of streams")
+
+    def parts(self):
+        return self._parts
+
+    @staticmethod
+    def _read_of(sub):
+        _, norm, conn, _ = sub
+        return conn.weights()[0], norm.weight, norm.eps
+
+    def first_read(self):
+        return self._read_of(self.sublayers[0])
+
+    def run(self, ctx, x, entry: int, pending=None, next_read=None):
+        """``pending``: the normed read of this block's first sublayer, if the block before made it.
+        Returns the normed read for ``next_read`` (that of the block after), or None."""
+        ops, s = ctx.ops, self.streams
+        fuse = bool(getattr(ops, "fuse_streams", False))
+        h = pending if pending is not None else ops.stream_step(x, s, read=self.first_read())
+        for i, (part, norm, conn, is_mixer) in enumerate(self.sublayers):
+            following = self._read_of(self.sublayers[i + 1]) if i + 1 < len(self.sublayers) else next_read
+            _, w_out, mix = conn.weights()
+            side_by_side = hasattr(part, "results")
+            if is_mixer:
+                ys, ws = part.results(ctx, h, entry) if side_by_side and fuse else ([part.forward(ctx, h, entry, accumulate_into=None)], None)
+            else:
+                ys, ws = [part.forward(ctx, h, accumulate_into=None)], None
+            eps = norm.eps
+            if fuse:
+                h = ops.stream_step(x, s, results=ys, result_norms=ws, norm_eps=eps, write=(mix, w_out), read=following)
+            else:
+                ops.stream_step(x, s, results=ys, write=(mix, w_out))
+                h = ops.stream_step(x, s, read=following) if following is not None else None
+        return h
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "multi_stream", StreamBlock)

@@ -12,7 +12,8 @@ from typing import Dict, List, Optional, Tuple
 
 
 #: the registry role of a block's well-known part names; other names carry their role in the PartSpec
-_ROLE_OF_NAME = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "ffn_norm": "norm"}
+_ROLE_OF_NAME = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "ffn_norm": "norm",
+                 "mixer_connection": "connection", "ffn_connection": "connection"}
 
 
 @dataclass
@@ -94,6 +95,9 @@ class ModelSpec:
     logit_scale: float = 1.0
     #: name patterns (fnmatch) of tensors a model folder may hold that the model does not use
     ignorable: List[str] = field(default_factory=list)
+    #: rows of residual state per token (1: the ordinary residual stream).  With more, the embedded row
+    #: is copied into each at the start and the rows are added up before the final norm.
+    residual_streams: int = 1
 
     def tensor_table(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
         """name -> (shape, init kind) of every tensor the model needs."""

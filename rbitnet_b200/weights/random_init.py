@@ -91,9 +91,10 @@ def reference_value(seed: int, name: str, index: int) -> float:
 
 def random_tensor(name: str, shape, kind: str, seed: int, dtype=torch.float32,
                   device="cpu") -> torch.Tensor:
-    """kind "matrix": N(0, 0.02); kind "norm": 1 + N(0, 0.02).  Values are made
+    """kind "matrix": N(0, 0.02); "norm": 1 + N(0, 0.02); "identity" (a square matrix): I + N(0, 0.02);
+    "share" (a vector of n): 1/n + N(0, 0.02); "taps" (rows of n): 1/n + N(0, 0.02).  Values are made
     in float32 and then rounded to ``dtype``."""
-    if kind not in ("matrix", "norm"):
+    if kind not in ("matrix", "norm", "identity", "share", "taps"):
         raise ValueError(f"unknown init kind {kind!r}")
     shape = tuple(int(s) for s in shape)
     n = math.prod(shape)
@@ -105,8 +106,13 @@ def random_tensor(name: str, shape, kind: str, seed: int, dtype=torch.float32,
         v = random_values(key, a, c, device) * scale
         if kind == "norm":
             v = v + 1.0
+        elif kind in ("share", "taps"):
+            v = v + 1.0 / shape[-1]
         out[a:a + c] = v.to(dtype)
-    return out.view(shape)
+    out = out.view(shape)
+    if kind == "identity":
+        out = (out.to(torch.float32) + torch.eye(shape[-1], dtype=torch.float32, device=device)).to(dtype)
+    return out
 
 
 def random_tensors(spec, seed: int, dtype=torch.float32, device="cpu") -> Dict[str, torch.Tensor]:

@@ -63,10 +63,147 @@ class TorchOps:
             return accumulate_into
         return y.to(out_dtype or self.dtype)
 
-    def gated_linear(self, x, weight):
+    def gated_linear(self, x, weight, act=None):
         gu = x.to(torch.float32) @ weight.w.to(torch.float32).T
         g, u = gu[:, :weight.inner], gu[:, weight.inner:]
+        if act is not None:
+            alpha, limit, shift = act
+            g, u = torch.clamp(g, max=limit), torch.clamp(u, -limit, limit)
+            return (g / (1.0 + torch.exp(-alpha * g)) * (u + shift)).to(self.dtype)
         return (g / (1.0 + torch.exp(-g)) * u).to(self.dtype)
+
+    def normed(self, rows):
+        return rows
+
+    # ---- several residual streams
+    fuse_streams = True
+
+    def streams_expand(self, x, s):
+        return x.repeat(1, s).contiguous()
+
+    def streams_sum(self, x, s):
+        R, E = x.shape[0], x.shape[1] // s
+        return x.view(R, s, E).sum(1)
+
+    def normed_mean(self, results, weights, eps):
+        out = 0.0
+        for y, w in zip(results, weights):
+            out = out + y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps) * w
+        return out / len(results)
+
+    def stream_step(self, x, s, results=None, result_norms=None, norm_eps=0.0, write=None, read=None, want_result=False):
+        T, E = x.shape[0], x.shape[1] // s
+        X = x.view(T, s, E)
+        y = None
+        if results:
+            y = self.normed_mean(results, result_norms, norm_eps) if result_norms else results[0]
+            mix, w_out = write
+            X.copy_(torch.einsum("kj,tke->tje", mix, X) + w_out[None, :, None] * y[:, None, :])
+        h = None
+        if read is not None:
+            w_in, norm_w, eps = read
+            u = torch.einsum("k,tke->te", w_in, X)
+            h = (u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps) * norm_w).to(self.dtype)
+        return (h, y) if want_result else h
+
+    # ---- attention with a projection norm, a partly turned head, a gate per head
+    def cache_head_width(self, head_dim, value_dim):
+        return max(head_dim, value_dim)
+
+    def norm_rotate_append(self, proj, table, meta, view, n_heads, head_dim, value_dim, q_norm_w, k_norm_w, eps):
+        T, H, D, Dv, Kh, Dc = proj.shape[0], n_heads, head_dim, value_dim, view.n_kv_heads, view.head_dim
+        x = proj.to(torch.float32)
+        q, k, v = x[:, :H * D], x[:, H * D:(H + Kh) * D], x[:, (H + Kh) * D:(H + Kh) * D + Kh * Dv]
+        if q_norm_w is not None:
+            q = q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps) * q_norm_w
+            k = k / torch.sqrt((k * k).mean(-1, keepdim=True) + eps) * k_norm_w
+        q, k, v = q.reshape(T, H, D).clone(), k.reshape(T, Kh, D).clone(), v.reshape(T, Kh, Dv)
+        if table is not None:
+            freq, magnitude, interleaved, rot = table
+            ang = meta.tok_pos.to(torch.float64)[:, None] * freq[None, :]
+            c, s_ = (torch.cos(ang) * magnitude).float()[:, None, :], (torch.sin(ang) * magnitude).float()[:, None, :]
+            for t_ in (q, k):
+                if interleaved:
+                    a, b = t_[..., 0:rot:2].clone(), t_[..., 1:rot:2].clone()
+                    t_[..., 0:rot:2], t_[..., 1:rot:2] = a * c - b * s_, b * c + a * s_
+                else:
+                    a, b = t_[..., :rot // 2].clone(), t_[..., rot // 2:rot].clone()
+                    t_[..., :rot // 2], t_[..., rot // 2:rot] = a * c - b * s_, b * c + a * s_
+        qo = torch.zeros(T, H, Dc)
+        qo[..., :D] = q
+        for t in range(T):
+            p, slot = int(meta.tok_pos[t]), int(meta.tok_slot[t])
+            page = int(view.page_table[slot, p // view.page_size])
+            view.k[page, :, p % view.page_size, :] = 0
+            view.v[page, :, p % view.page_size, :] = 0
+            view.k[page, :, p % view.page_size, :D] = k[t].to(view.k.dtype)
+            view.v[page, :, p % view.page_size, :Dv] = v[t].to(view.v.dtype)
+        return qo.to(self.dtype)
+
+    def head_gate(self, a, proj, gate_column, n_heads, value_dim, cache_width):
+        T = a.shape[0]
+        out = a.to(torch.float32).view(T, n_heads, cache_width)[:, :, :value_dim]
+        if gate_column is not None:
+            out = out * torch.sigmoid(proj[:, gate_column:gate_column + n_heads].to(torch.float32))[:, :, None]
+        return out.reshape(T, n_heads * value_dim).to(self.dtype)
+
+    # ---- recurrent mixers
+    @staticmethod
+    def _runs(meta):
+        return [(c.offset, c.n_new, c.slot) for c in meta.seqs]
+
+    def gated_recurrence(self, proj, p, state, meta):
+        W, B, K = p.inner, p.blocks, p.taps
+        Wb = W // B
+        f = p.f32
+        out = torch.zeros(proj.shape[0], W)
+        sp = p.decay_scale * torch.nn.functional.softplus(f["lam"])
+        for first, n, slot in self._runs(meta):
+            xx = proj[first:first + n, :W].float() + f["x.b"]
+            y = proj[first:first + n, W:].float() + f["y.b"]
+            y = 0.5 * y * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (y + 0.044715 * y ** 3)))
+            old = state["tail"][slot] if K > 1 else torch.zeros(0, W)
+            hist = torch.cat([old, xx], dim=0)                    # K-1 earlier inputs, then this run's
+            S = state["S"][slot].clone()
+            for t in range(n):
+                u = f["conv.b"] + (hist[t:t + K] * f["conv"].T).sum(0)
+                ub = u.view(B, Wb)
+                g = torch.einsum("boi,bi->bo", p.w_gates, ub)     # [B, 2 Wb]
+                r = torch.sigmoid(g[:, :Wb].reshape(W) + f["ra.b"].reshape(W))
+                i = torch.sigmoid(g[:, Wb:].reshape(W) + f["ri.b"].reshape(W))
+                a = torch.exp(-sp * r)
+                S = a * S + torch.sqrt(1.0 - a * a) * i * u
+                out[first + t] = S * y[t]
+            state["S"][slot] = S
+            if K > 1:
+                state["tail"][slot] = hist[n:n + K - 1]
+        return out.to(self.dtype)
+
+    def matrix_memory(self, proj, p, state, meta):
+        H, D, Dv, cap = p.n_heads, p.head_dim, p.value_dim, p.gate_cap
+        at = p.offsets()
+        x = proj.float()
+        T = x.shape[0]
+        o = torch.zeros(T, H, Dv)
+        for first, n, slot in self._runs(meta):
+            C, nn, m = state["C"][slot].clone(), state["n"][slot].clone(), state["m"][slot].clone()
+            for t in range(first, first + n):
+                q = x[t, at["q"]:at["q"] + H * D].view(H, D) * D ** -0.5
+                k = x[t, at["k"]:at["k"] + H * D].view(H, D)
+                v = x[t, at["v"]:at["v"] + H * Dv].view(H, Dv)
+                ig = cap * torch.tanh((x[t, at["i"]:at["i"] + H] + p.i_bias) / cap)
+                fg = torch.nn.functional.logsigmoid(cap * torch.tanh((x[t, at["f"]:at["f"] + H] + p.f_bias) / cap))
+                m_new = torch.maximum(fg + m, ig)
+                keep, take = torch.exp(fg + m - m_new), torch.exp(ig - m_new)
+                C = keep[:, None, None] * C + take[:, None, None] * k[:, :, None] * v[:, None, :]
+                nn = keep[:, None] * nn + take[:, None] * k
+                m = m_new
+                den = torch.maximum((nn * q).sum(-1).abs(), torch.exp(-m)) + p.floor
+                o[t] = torch.einsum("hdv,hd->hv", C, q) / den[:, None]
+            state["C"][slot], state["n"][slot], state["m"][slot] = C, nn, m
+        o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + p.norm_eps)
+        g = torch.sigmoid(x[:, at["g"]:at["g"] + H * Dv])
+        return (o.reshape(T, H * Dv) * p.norm_w * g).to(self.dtype)
 
     def project_rotate_append(self, h, weight, rotary, meta, view, n_heads):
         return self.rotate_append(self.linear(h, weight), rotary, meta, view, n_heads)
