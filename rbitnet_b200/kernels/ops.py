@@ -541,7 +541,7 @@ class CudaOps:
         T = a.shape[0]
         out = torch.empty((T, n_heads * value_dim), dtype=self.dtype, device=self.device)
         gate = c_void_p(proj.data_ptr() + gate_column * proj.element_size()) if gate_column is not None else c_void_p(0)
-        self.lib.call("rb_head_gate", _ptr(out), _ptr(a), gate, proj.stride(0), self.code, T, n_heads, value_dim,
+        self.lib.call("rb_head_gate", _ptr(out), _ptr(a), gate, proj.stride(0) if proj is not None else 0, self.code, T, n_heads, value_dim,
                       cache_width, self._stream())
         return out
 
