@@ -173,7 +173,7 @@ def time_generate(engine, batch, context, steps, warmup):
     before, so this is not the plain step of ``e2e``; it is reported beside it."""
     import torch
     g = torch.Generator().manual_seed(2)
-    prompts = [torch.randint(0, engine.config.vocab_size, (context,), generator=g).tolist() for _ in range(batch)]
+    prompts = [torch.randint(0, engine.model.vocab_size, (context,), generator=g).tolist() for _ in range(batch)]
     stamps = []
 
     def on_token(request, token):
@@ -191,7 +191,7 @@ def time_generate(engine, batch, context, steps, warmup):
 def time_prefill(engine, tokens, reps=3):
     import torch
     from rbitnet_b200 import StepEntry
-    ids = torch.randint(0, engine.config.vocab_size, (tokens,), generator=torch.Generator().manual_seed(1)).tolist()
+    ids = torch.randint(0, engine.model.vocab_size, (tokens,), generator=torch.Generator().manual_seed(1)).tolist()
     times = []
     for r in range(reps + 1):
         s = engine.new_sequence()
@@ -487,6 +487,128 @@ def kernel_tables(engine, batch, ctx, prefill_tokens, pk, reps=5):
     return out
 
 
+# ---------------------------------------------------------------- --design: another design beside the closest Llama of equal size
+def _safuvik_shape(width, heads, kv, dim, vdim, window, rec_blocks, mem_heads, mem_dim, mem_vdim, ff, layers, vocab=32000,
+                   streams=4):
+    """Layer sizes in the manner of a real model: `layers` layers, every third one a matrix memory, the others
+    window attention beside a gated linear recurrence of the model's width."""
+    left = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "mask": {"size": window},
+            "rot": {"base": 10000.0, "dims": dim // 2, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    par = {"type": "parallel", "mixer": {"left": left, "right": {"width": width, "blocks": rec_blocks, "conv": 4}},
+           "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}}
+    mem = {"type": "mlstm", "mixer": {"heads": mem_heads, "dim": mem_dim, "vdim": mem_vdim, "gate_cap": 15.0},
+           "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}}
+    return {"architecture": "Safuvik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "streams": streams,
+            "logit_scale": 1.0, "max_positions": 8192, "layers": [mem if i % 3 == 2 else par for i in range(layers)]}
+
+
+def _llama_like(width, heads, kv, dim, ff, layers, vocab=32000):
+    return dict(architectures=["LlamaForCausalLM"], num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                num_key_value_heads=kv, head_dim=dim, intermediate_size=ff, vocab_size=vocab, rope_theta=10000.0,
+                rms_norm_eps=1e-6, max_position_embeddings=8192, tie_word_embeddings=False, hidden_act="silu")
+
+
+DESIGN_SIZES = {
+    # name: (Safuvik configuration, Llama configuration of equal width, layers, feed-forward and attention heads)
+    "w2048": (_safuvik_shape(2048, 16, 4, 128, 64, 1024, 16, 8, 128, 256, 5632, 6), _llama_like(2048, 16, 4, 128, 5632, 6)),
+    "w4096": (_safuvik_shape(4096, 32, 8, 128, 128, 1024, 16, 8, 256, 512, 14336, 3), _llama_like(4096, 32, 8, 128, 14336, 3)),
+}
+
+
+class DesignTimer(KernelTimer):
+    """KernelTimer with the operations of the recurrent mixers and of the residual streams."""
+    OPS = KernelTimer.OPS + ("stream_step", "normed_mean", "streams_expand", "streams_sum", "norm_rotate_append", "head_gate",
+                             "gated_recurrence", "matrix_memory")
+
+    @staticmethod
+    def _describe(name, a, kw, sync=True):
+        el = lambda t: t.numel() * t.element_size()
+        if name == "stream_step":
+            x, s = a[0], a[1]
+            T, E = x.shape[0], x.shape[1] // s
+            res = kw.get("results") or []
+            nbytes = el(x) * (2 if res else 1) + sum(el(r) for r in res) + (T * E * 2 if kw.get("read") is not None else 0)
+            what = "+".join(w for w, on in (("results' norms and mean", bool(kw.get("result_norms"))), ("write", bool(res)),
+                                            ("read+norm", kw.get("read") is not None)) if on)
+            return f"residual streams: {what} [{T} rows, {s}x{E}]", nbytes, 0.0
+        if name == "norm_rotate_append":
+            proj, view, H = a[0], a[3], a[4]
+            T = proj.shape[0]
+            return (f"q/k norm + rotation + append [{T} rows of {proj.shape[1]}]",
+                    el(proj) + T * (H + 2 * view.n_kv_heads) * view.head_dim * proj.element_size(), 0.0)
+        if name == "head_gate":
+            return f"head gate [{a[0].shape[0]} rows]", 2 * el(a[0]), 0.0
+        if name == "gated_recurrence":
+            proj, p = a[0], a[1]
+            T, W = proj.shape[0], p.inner
+            return (f"gated linear recurrence: convolution, gates, scan [{T} rows, {W} channels, {p.blocks} blocks]",
+                    el(proj) + T * W * 2 + el(p.w_gates), 0.0)
+        if name == "matrix_memory":
+            proj, p = a[0], a[1]
+            T = proj.shape[0]
+            return (f"matrix memory: recurrence, head norm and gate [{T} rows, {p.n_heads} heads of {p.head_dim}x{p.value_dim}]",
+                    el(proj) + T * p.n_heads * p.value_dim * 2, 0.0)
+        if name in ("normed_mean", "streams_expand", "streams_sum"):
+            t = a[0][0] if name == "normed_mean" else a[0]
+            return f"{name} [{t.shape[0]} rows]", 3 * el(t), 0.0
+        return KernelTimer._describe(name, a, kw, sync)
+
+
+def run_design(name, args):
+    """Prefill and decode throughput of the Safuvik design beside the Llama decoder of equal width, layers and
+    feed-forward size, and the time of every operation of one prefill step with its share of the roofline."""
+    import torch
+    from rbitnet_b200 import Engine, StepEntry
+    pk = peaks()
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+    out = {"design": "Safuvik beside Llama", "size": name, "peaks": pk, "dtype": "bf16", "data": "synthetic (random weights)",
+           "batch": args.batch, "context": args.context, "prefill_tokens": args.prefill_tokens, "models": {}}
+    for label, cfg in zip(("safuvik", "llama"), DESIGN_SIZES[name]):
+        room = steps + warmup + 16
+        ctx = args.context
+        max_tokens = max(args.batch * (-(-(ctx + room) // 64) * 64), args.prefill_tokens + 64) + 64 * 8
+        engine = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens, max_seq=8192, max_batch=64)
+        for g in engine.cache.groups:
+            for pool in g.pools:
+                pool.normal_(0.0, 1.0)
+        torch.cuda.synchronize()
+        pf_ms = time_prefill(engine, args.prefill_tokens)
+        ms, launches, _ = time_decode(engine, args.batch, ctx, steps, warmup)
+        nbytes = decode_bytes(engine, args.batch, ctx if label == "llama" else min(ctx, 1024))
+        rec = {"layers": len(engine.spec.layers), "width": engine.spec.width,
+               "prefill_ms": round(pf_ms, 3), "prefill_tokens_per_s": round(args.prefill_tokens / pf_ms * 1e3, 1),
+               "decode_ms_per_step": round(ms, 4), "decode_tokens_per_s": round(args.batch / ms * 1e3, 1),
+               "decode_launches_per_step": launches // steps,
+               "decode_bytes_per_step": nbytes, "decode_frac_of_hbm": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+        # one prefill step, operation by operation
+        ids = torch.randint(0, engine.model.vocab_size, (args.prefill_tokens,), generator=torch.Generator().manual_seed(1)).tolist()
+        reps = 3
+        with DesignTimer(engine.ops) as timer:
+            for r in range(reps + 1):
+                if r == 1:
+                    torch.cuda.synchronize()
+                    timer.records.clear()
+                s = engine.new_sequence()
+                engine.step([StepEntry(s, ids, [len(ids) - 1])])
+                engine.end_sequence(s)
+            rows, total = timer.table(pk, reps)
+        rec["prefill_operations"] = rows
+        rec["prefill_sum_of_operations_us"] = round(total, 1)
+        out["models"][label] = rec
+        del engine
+        torch.cuda.empty_cache()
+    print(json.dumps(out))
+    for label, rec in out["models"].items():
+        print(f"\n{label} {name}: prefill {rec['prefill_tokens_per_s']:.0f} tok/s ({rec['prefill_ms']:.2f} ms), decode "
+              f"{rec['decode_tokens_per_s']:.0f} tok/s ({rec['decode_ms_per_step']:.3f} ms, {rec['decode_launches_per_step']} launches)",
+              file=sys.stderr)
+        print(f"{'us':>9} {'calls':>6} {'share':>6} {'GB/s':>8} {'TFLOP/s':>8} {'bound':>6} {'frac':>6}  operation", file=sys.stderr)
+        for r in rec["prefill_operations"]:
+            print(f"{r['us']:9.1f} {r['calls_per_step']:6.1f} {r['share_of_step']:6.3f} {r['gb_s']:8.1f} {r['tflop_s']:8.2f} "
+                  f"{r['bound']:>6} {r['frac']:6.3f}  {r['kernel']}", file=sys.stderr)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -513,6 +635,9 @@ def main():
                          "are those of the generation workloads and are named in metric and config)")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="run one of the other generation workloads end to end instead (one short line)")
+    ap.add_argument("--design", default=None, choices=sorted(DESIGN_SIZES),
+                    help="instead of the headline: prefill and decode of the Safuvik design beside the Llama decoder of "
+                         "equal size at these layer sizes (uses --batch, --context, --prefill-tokens, --steps)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -525,6 +650,8 @@ def main():
         return 2
     if args.workload:
         return run_workload(args.workload)
+    if args.design:
+        return run_design(args.design, args)
     steps, warmup = max(1, args.steps), max(3, args.warmup)
 
     import torch

@@ -92,6 +92,82 @@ __global__ void __launch_bounds__(64) gated_scan_kernel(
   for (int k = 0; k < K - 1; ++k) tail[((int64_t)slot * (K - 1) + k) * W + c] = keep[k];
 }
 
+// ---- long runs: the gates become decays and drives in one pass over all rows, then a scan in chunks of time
+// a = exp(-c softplus(lam) sigmoid(g_r + b_r)) replaces g_r and b = sqrt(1 - a^2) sigmoid(g_i + b_i) u replaces g_i, in place.
+__global__ void gate_prepare_kernel(float* __restrict__ gates, const float* __restrict__ u, const float* __restrict__ gate_r_bias,
+                                    const float* __restrict__ gate_i_bias, const float* __restrict__ lam, float decay_scale,
+                                    int64_t n, int W, int Wb) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / W;
+    const int c = (int)(i % W);
+    const int blk = c / Wb, o = c % Wb;
+    float* g = gates + (t * (W / Wb) + blk) * 2 * Wb;
+    const float r = sigmoidf_(g[o] + gate_r_bias[c]);
+    const float in = sigmoidf_(g[Wb + o] + gate_i_bias[c]);
+    const float a = expf(-decay_scale * softplusf_(lam[c]) * r);
+    g[o] = a;
+    g[Wb + o] = sqrtf(1.0f - a * a) * in * u[i];
+  }
+}
+
+// One block per (run, 32 channels): 32 lanes are 32 channels (rows of the inputs are read 128 bytes at a time),
+// the block's 32 warps are 32 chunks of the run's time.  Every warp first folds its chunk into (A, B) with
+// S_end = A S_begin + B, the chunks' pairs are chained in shared memory, and a second pass over the chunk
+// writes S_t * gelu_tanh(y_t).
+constexpr int SCAN_CH = 32, SCAN_CHUNKS = 32;
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(SCAN_CH * SCAN_CHUNKS) gated_scan_chunked_kernel(
+    TO* __restrict__ out, const float* __restrict__ ab, const TI* __restrict__ xy, int64_t ldxy, int x_off, int y_off,
+    const float* __restrict__ x_bias, const float* __restrict__ y_bias, float* __restrict__ state, float* __restrict__ tail,
+    const int* __restrict__ seq_first, const int* __restrict__ seq_count, const int* __restrict__ tok_slot, int W, int Wb, int K) {
+  rb_pdl_launch_dependents();
+  __shared__ float sA[SCAN_CHUNKS][SCAN_CH], sB[SCAN_CHUNKS][SCAN_CH];
+  const int lane = threadIdx.x & 31, chunk = threadIdx.x >> 5;
+  const int c = blockIdx.y * SCAN_CH + lane;
+  const bool live = c < W;
+  const int cc = live ? c : 0;
+  const float yb = y_bias != nullptr ? y_bias[cc] : 0.f;
+  const float xb = x_bias != nullptr ? x_bias[cc] : 0.f;
+  const int blk = cc / Wb, o = cc % Wb;
+  rb_pdl_wait();
+  const int first = seq_first[blockIdx.x], n = seq_count[blockIdx.x];
+  const int slot = tok_slot[first];
+  const int L = (n + SCAN_CHUNKS - 1) / SCAN_CHUNKS;
+  const int t0 = first + min(n, chunk * L), t1 = first + min(n, (chunk + 1) * L);
+  const int nb = W / Wb;
+  float A = 1.f, B = 0.f;
+  for (int t = t0; t < t1; ++t) {
+    const float* g = ab + ((int64_t)t * nb + blk) * 2 * Wb;
+    const float a = g[o], b = g[Wb + o];
+    B = fmaf(a, B, b);
+    A *= a;
+  }
+  sA[chunk][lane] = A;
+  sB[chunk][lane] = B;
+  __syncthreads();
+  float S = live ? state[(int64_t)slot * W + cc] : 0.f;
+  for (int k = 0; k < chunk; ++k) S = fmaf(sA[k][lane], S, sB[k][lane]);
+  for (int t = t0; t < t1; ++t) {
+    const float* g = ab + ((int64_t)t * nb + blk) * 2 * Wb;
+    S = fmaf(g[o], S, g[Wb + o]);
+    const float y = gelu_tanh_(rb_to_float<TI>(xy[(int64_t)t * ldxy + y_off + cc]) + yb);
+    if (live) out[(int64_t)t * W + cc] = rb_from_float<TO>(S * y);
+  }
+  if (!live) return;
+  if (chunk == SCAN_CHUNKS - 1) state[(int64_t)slot * W + cc] = S;       // the last chunk ends where the run ends
+  if (chunk == 0) {
+    float keep[8];
+    for (int k = 0; k < K - 1; ++k) {
+      const int back = K - 2 - k;
+      keep[k] = back < n ? rb_to_float<TI>(xy[(int64_t)(first + n - 1 - back) * ldxy + x_off + cc]) + xb
+                         : tail[((int64_t)slot * (K - 1) + (k + n)) * W + cc];
+    }
+    for (int k = 0; k < K - 1; ++k) tail[((int64_t)slot * (K - 1) + k) * W + cc] = keep[k];
+  }
+}
+
 // ---------------------------------------------------------------- matrix memory
 // One block per (run, head, tile of value columns).  A thread owns one value column j and every P-th
 // row d of the memory (R rows at most), so a token costs it 2 R multiply-adds and the sums over d are
@@ -100,9 +176,19 @@ __global__ void __launch_bounds__(64) gated_scan_kernel(
 constexpr int MM_THREADS = 128;
 constexpr int MM_TT = 16;
 
-template <typename TI, int R>
+__device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// The projections are float32 rows.  A tile of TT tokens (q, k, the block's value columns, the two gate
+// pre-activations) is copied into one of two shared buffers with cp.async while the tile before it is
+// worked on, so the loop over tokens never waits for global memory.
+template <int R>
 __global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(
-    float* __restrict__ o_out, const TI* __restrict__ proj, int64_t ld, int q_off, int k_off, int v_off, int i_off,
+    float* __restrict__ o_out, const float* __restrict__ proj, int64_t ld, int q_off, int k_off, int v_off, int i_off,
     int f_off, const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap, float q_scale,
     float floor_add, float* __restrict__ C_state, float* __restrict__ n_state, float* __restrict__ m_state,
     const int* __restrict__ seq_first, const int* __restrict__ seq_count, const int* __restrict__ tok_slot, int H, int D,
@@ -110,11 +196,7 @@ __global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(
   rb_pdl_launch_dependents();
   extern __shared__ __align__(16) float sm[];
   const int cols = MM_THREADS / P;
-  float* s_q = sm;                       // [TT][D]
-  float* s_k = s_q + MM_TT * D;          // [TT][D]
-  float* s_v = s_k + MM_TT * D;          // [TT][cols]
-  float* s_i = s_v + MM_TT * cols;       // [TT]
-  float* s_f = s_i + MM_TT;              // [TT]
+  const int tile_floats = MM_TT * (2 * D + cols + 2);
   const int h = blockIdx.y;
   const int col = threadIdx.x / P, part = threadIdx.x % P;
   const int j = blockIdx.z * cols + col;
@@ -124,6 +206,34 @@ __global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(
   const int first = seq_first != nullptr ? seq_first[blockIdx.x] : blockIdx.x;
   const int n = seq_count != nullptr ? seq_count[blockIdx.x] : 1;
   const int slot = tok_slot[first];
+
+  auto stage = [&](int t0, int buf) {
+    float* s_q = sm + buf * tile_floats;
+    float* s_k = s_q + MM_TT * D;
+    float* s_v = s_k + MM_TT * D;
+    float* s_g = s_v + MM_TT * cols;            // [TT][2]: input gate, forget gate (pre-activations)
+    const int nt = min(MM_TT, n - t0);
+    for (int e = threadIdx.x; e < nt * D; e += MM_THREADS) {
+      const int tt = e / D, d = e % D;
+      const float* row = proj + (int64_t)(first + t0 + tt) * ld;
+      cp_async_f32(s_q + e, row + q_off + h * D + d);
+      cp_async_f32(s_k + e, row + k_off + h * D + d);
+    }
+    for (int e = threadIdx.x; e < nt * cols; e += MM_THREADS) {
+      const int tt = e / cols, cc = e % cols;
+      const int jj = blockIdx.z * cols + cc;
+      if (jj < Dv) cp_async_f32(s_v + e, proj + (int64_t)(first + t0 + tt) * ld + v_off + h * Dv + jj);
+      else s_v[e] = 0.f;
+    }
+    for (int tt = threadIdx.x; tt < nt; tt += MM_THREADS) {
+      const float* row = proj + (int64_t)(first + t0 + tt) * ld;
+      cp_async_f32(s_g + 2 * tt, row + i_off + h);
+      cp_async_f32(s_g + 2 * tt + 1, row + f_off + h);
+    }
+    cp_async_commit();
+  };
+
+  stage(0, 0);
   float Cr[R], nr[R];
   float* Cs = C_state + ((int64_t)slot * H + h) * D * Dv;
   float* ns = n_state + ((int64_t)slot * H + h) * D;
@@ -134,30 +244,29 @@ __global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(
     nr[r] = d < D ? ns[d] : 0.f;
   }
   float m = m_state[(int64_t)slot * H + h];
-  for (int t0 = 0; t0 < n; t0 += MM_TT) {
+  int buf = 0;
+  for (int t0 = 0; t0 < n; t0 += MM_TT, buf ^= 1) {
     const int nt = min(MM_TT, n - t0);
+    if (t0 + MM_TT < n) {
+      stage(t0 + MM_TT, buf ^ 1);        // the buffer that the tile before this one used: everybody left it at the last barrier
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
     __syncthreads();
-    for (int e = threadIdx.x; e < nt * D; e += MM_THREADS) {
-      const int tt = e / D, d = e % D;
-      const TI* row = proj + (int64_t)(first + t0 + tt) * ld;
-      s_q[tt * D + d] = rb_to_float<TI>(row[q_off + h * D + d]) * q_scale;
-      s_k[tt * D + d] = rb_to_float<TI>(row[k_off + h * D + d]);
-    }
-    for (int e = threadIdx.x; e < nt * cols; e += MM_THREADS) {
-      const int tt = e / cols, cc = e % cols;
-      const int jj = blockIdx.z * cols + cc;
-      s_v[tt * cols + cc] = jj < Dv ? rb_to_float<TI>(proj[(int64_t)(first + t0 + tt) * ld + v_off + h * Dv + jj]) : 0.f;
-    }
-    for (int tt = threadIdx.x; tt < nt; tt += MM_THREADS) {
-      const TI* row = proj + (int64_t)(first + t0 + tt) * ld;
-      const float ip = rb_to_float<TI>(row[i_off + h]) + ib, fp = rb_to_float<TI>(row[f_off + h]) + fb;
+    float* s_q = sm + buf * tile_floats;
+    float* s_k = s_q + MM_TT * D;
+    float* s_v = s_k + MM_TT * D;
+    float* s_g = s_v + MM_TT * cols;
+    if (threadIdx.x < nt) {
+      const float ip = s_g[2 * threadIdx.x] + ib, fp = s_g[2 * threadIdx.x + 1] + fb;
       const float fc = cap * tanhf(fp / cap);
-      s_i[tt] = cap * tanhf(ip / cap);
-      s_f[tt] = fminf(fc, 0.f) - log1pf(expf(-fabsf(fc)));       // log sigmoid
+      s_g[2 * threadIdx.x] = cap * tanhf(ip / cap);
+      s_g[2 * threadIdx.x + 1] = fminf(fc, 0.f) - log1pf(expf(-fabsf(fc)));       // log sigmoid
     }
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
-      const float ig = s_i[tt], fg = s_f[tt];
+      const float ig = s_g[2 * tt], fg = s_g[2 * tt + 1];
       const float m_new = fmaxf(fg + m, ig);
       const float keep = expf(fg + m - m_new), take = expf(ig - m_new);
       m = m_new;
@@ -179,10 +288,11 @@ __global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(
         nq += __shfl_xor_sync(0xffffffffu, nq, off);
       }
       if (live && part == 0) {
-        const float den = fmaxf(fabsf(nq), expf(-m)) + floor_add;
-        o_out[(int64_t)(first + t0 + tt) * H * Dv + h * Dv + j] = num / den;
+        const float den = fmaxf(fabsf(nq * q_scale), expf(-m)) + floor_add;
+        o_out[(int64_t)(first + t0 + tt) * H * Dv + h * Dv + j] = num * q_scale / den;
       }
     }
+    __syncthreads();                       // the buffer may be filled again
   }
 #pragma unroll
   for (int r = 0; r < R; ++r) {
@@ -237,14 +347,36 @@ RB_EXPORT int rb_conv_causal(float* u, const void* x, int64_t ldx, int x_off, in
   return 0;
 }
 
+// With seq_first and seq_count (runs of several rows; n_rows: all rows of the step) the gates buffer is overwritten.
 RB_EXPORT int rb_gated_scan(void* out, int out_dtype, const float* u, const float* gates, const float* gate_r_bias,
                             const float* gate_i_bias, const float* lam, float decay_scale, const void* xy, int64_t ldxy,
                             int xy_dtype, int x_off, int y_off, const float* x_bias, const float* y_bias, float* state,
-                            float* tail, const int* seq_first, const int* seq_count, const int* tok_slot, int n_seq, int W,
-                            int Wb, int K, cudaStream_t stream) {
+                            float* tail, const int* seq_first, const int* seq_count, const int* tok_slot, int n_seq, int n_rows,
+                            int W, int Wb, int K, cudaStream_t stream) {
   if (n_seq == 0) return 0;
   RB_REQUIRE(W > 0 && Wb > 0 && W % Wb == 0, "rb_gated_scan: width %d is not made of blocks of %d", W, Wb);
   RB_REQUIRE(K >= 1 && K <= 9, "rb_gated_scan: %d taps (1..9 are built)", K);
+  if (seq_first != nullptr && seq_count != nullptr) {
+    // runs of several rows (a prompt, or a portion of one): decays and drives for all rows at once, then the chunked scan
+    RB_REQUIRE(n_rows > 0, "rb_gated_scan: runs of several rows need the number of rows");
+    const int64_t n = (int64_t)n_rows * W;
+    const int64_t most = (int64_t)rb_sm_count() * 16;
+    const int blocks = (int)((n + 255) / 256 < most ? (n + 255) / 256 : most);
+    RB_LAUNCH("gate_prepare_kernel", (gate_prepare_kernel), blocks, 256, 0, stream, (float*)gates, u, gate_r_bias, gate_i_bias,
+              lam, decay_scale, n, W, Wb);
+    const dim3 cgrid(n_seq, (W + SCAN_CH - 1) / SCAN_CH);
+#define CLAUNCH(TI, TO)                                                                                              \
+  RB_LAUNCH("gated_scan_chunked_kernel", (gated_scan_chunked_kernel<TI, TO>), cgrid, SCAN_CH * SCAN_CHUNKS, 0, stream, \
+            (TO*)out, gates, (const TI*)xy, ldxy, x_off, y_off, x_bias, y_bias, state, tail, seq_first, seq_count,   \
+            tok_slot, W, Wb, K)
+    if (xy_dtype == RB_F32 && out_dtype == RB_F32) CLAUNCH(float, float);
+    else if (xy_dtype == RB_F32 && out_dtype == RB_BF16) CLAUNCH(float, __nv_bfloat16);
+    else if (xy_dtype == RB_BF16 && out_dtype == RB_BF16) CLAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else RB_FAIL("rb_gated_scan: unsupported dtypes %d -> %d", xy_dtype, out_dtype);
+#undef CLAUNCH
+    RB_CHECK_LAUNCH("rb_gated_scan");
+    return 0;
+  }
   const dim3 grid(n_seq, (W + 63) / 64);
 #define LAUNCH(TI, TO)                                                                                              \
   RB_LAUNCH("gated_scan_kernel", (gated_scan_kernel<TI, TO>), grid, 64, 0, stream, (TO*)out, u, gates, gate_r_bias,  \
@@ -259,10 +391,11 @@ RB_EXPORT int rb_gated_scan(void* out, int out_dtype, const float* u, const floa
   return 0;
 }
 
-// Lanes per value column for a memory of D rows: the smallest power of two that leaves a thread at most 32 rows.
+// Lanes per value column for a memory of D rows: the smallest power of two that leaves a thread at most 16 rows
+// (32 rows beyond 512, where a warp's 32 lanes are all a column has).
 RB_EXPORT int rb_matrix_memory_lanes(int D) {
   int P = 1;
-  while ((D + P - 1) / P > 32 && P < 32) P *= 2;
+  while ((D + P - 1) / P > 16 && P < 32) P *= 2;
   return P;
 }
 
@@ -274,27 +407,22 @@ RB_EXPORT int rb_matrix_memory(float* o_out, const void* proj, int64_t ld, int p
   if (n_seq == 0) return 0;
   RB_REQUIRE(H > 0 && D > 0 && Dv > 0 && D <= 1024, "rb_matrix_memory: bad sizes H=%d D=%d Dv=%d (D up to 1024)", H, D, Dv);
   RB_REQUIRE(cap > 0.f, "rb_matrix_memory: the gates' cap must be positive");
+  RB_REQUIRE(proj_dtype == RB_F32, "rb_matrix_memory: the projections are float32 rows (found dtype %d)", proj_dtype);
   const int P = rb_matrix_memory_lanes(D);
   const int per = (D + P - 1) / P;
   const int cols = MM_THREADS / P;
   const dim3 grid(n_seq, H, (Dv + cols - 1) / cols);
   RB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "rb_matrix_memory: grid %d x %d", grid.y, grid.z);
-  const size_t smem = (size_t)(MM_TT * (2 * D + cols + 2)) * sizeof(float);
-#define LAUNCH(TI, RR)                                                                                              \
+  const size_t smem = (size_t)(2 * MM_TT * (2 * D + cols + 2)) * sizeof(float);
+#define LAUNCH(RR)                                                                                                  \
   do {                                                                                                              \
     if (smem > 48 * 1024)                                                                                           \
-      RB_CUDA(cudaFuncSetAttribute(matrix_memory_kernel<TI, RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    RB_LAUNCH("matrix_memory_kernel", (matrix_memory_kernel<TI, RR>), grid, MM_THREADS, smem, stream, o_out,        \
-              (const TI*)proj, ld, q_off, k_off, v_off, i_off, f_off, i_bias, f_bias, cap, q_scale, floor_add,      \
+      RB_CUDA(cudaFuncSetAttribute(matrix_memory_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    RB_LAUNCH("matrix_memory_kernel", (matrix_memory_kernel<RR>), grid, MM_THREADS, smem, stream, o_out,            \
+              (const float*)proj, ld, q_off, k_off, v_off, i_off, f_off, i_bias, f_bias, cap, q_scale, floor_add,   \
               C_state, n_state, m_state, seq_first, seq_count, tok_slot, H, D, Dv, P);                              \
   } while (0)
-  if (proj_dtype == RB_F32) {
-    if (per <= 16) LAUNCH(float, 16); else LAUNCH(float, 32);
-  } else if (proj_dtype == RB_BF16) {
-    if (per <= 16) LAUNCH(__nv_bfloat16, 16); else LAUNCH(__nv_bfloat16, 32);
-  } else {
-    RB_FAIL("rb_matrix_memory: unknown dtype %d", proj_dtype);
-  }
+  if (per <= 16) LAUNCH(16); else LAUNCH(32);
 #undef LAUNCH
   RB_CHECK_LAUNCH("rb_matrix_memory");
   return 0;

@@ -16,7 +16,7 @@
 
 namespace {
 
-constexpr int MAX_STREAMS = 8;
+constexpr int MAX_STREAMS = 16;
 constexpr int MAX_Y = 4;
 
 struct StreamStepArgs {
@@ -34,15 +34,20 @@ struct StreamStepArgs {
   float* y_out;                  // optional [T, E]: the combined y, for whoever wants it alone
 };
 
-template <typename TO>
+// S > 0: the number of streams is known when the kernel is compiled (loops unroll without tests); S == 0: any
+// number up to MAX_STREAMS.  VEC == 4: rows are read and written four values at a time (E a multiple of 4,
+// 16-byte aligned pointers).
+template <typename TO, int S, int VEC>
 __global__ void __launch_bounds__(256) stream_step_kernel(StreamStepArgs a) {
   rb_pdl_launch_dependents();
+  constexpr int SS = S > 0 ? S : MAX_STREAMS;
   __shared__ float scratch[33];
-  __shared__ float s_mix[MAX_STREAMS * MAX_STREAMS], s_out[MAX_STREAMS], s_in[MAX_STREAMS];
+  __shared__ float s_mix[SS * SS], s_out[SS], s_in[SS];
   extern __shared__ __align__(16) float urow[];     // E floats: the next read's mix
-  const int t = blockIdx.x, s = a.s, E = a.E;
+  const int t = blockIdx.x, s = S > 0 ? S : a.s, E = a.E;
   // the small tables are weights: they do not depend on the kernel before
-  if (threadIdx.x < s * s && a.n_y > 0 && a.mix != nullptr) s_mix[threadIdx.x] = a.mix[threadIdx.x];
+  if (a.n_y > 0 && a.mix != nullptr)
+    for (int i = threadIdx.x; i < s * s; i += blockDim.x) s_mix[i] = a.mix[i];
   if (threadIdx.x < s) {
     s_out[threadIdx.x] = (a.n_y > 0 && a.w_out != nullptr) ? a.w_out[threadIdx.x] : 0.f;
     s_in[threadIdx.x] = a.w_in != nullptr ? a.w_in[threadIdx.x] : 0.f;
@@ -57,7 +62,14 @@ __global__ void __launch_bounds__(256) stream_step_kernel(StreamStepArgs a) {
     if (normed && k < a.n_y) {
       const float* yr = a.y[k] + (int64_t)t * E;
       float ss = 0.f;
-      for (int e = threadIdx.x; e < E; e += blockDim.x) ss += yr[e] * yr[e];
+      if (VEC == 4) {
+        for (int e = threadIdx.x * 4; e < E; e += blockDim.x * 4) {
+          const float4 v = *reinterpret_cast<const float4*>(yr + e);
+          ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+      } else {
+        for (int e = threadIdx.x; e < E; e += blockDim.x) ss += yr[e] * yr[e];
+      }
       ss = rb_block_sum(ss, scratch);
       yfac[k] = 1.0f / sqrtf(ss / (float)E + a.eps);
     }
@@ -65,44 +77,78 @@ __global__ void __launch_bounds__(256) stream_step_kernel(StreamStepArgs a) {
   __syncthreads();
   float* Xt = a.X + (int64_t)t * s * E;
   float ss = 0.f;
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    float xs[MAX_STREAMS];
+  for (int e = threadIdx.x * VEC; e < E; e += blockDim.x * VEC) {
+    float xs[SS][VEC];
 #pragma unroll
-    for (int k = 0; k < MAX_STREAMS; ++k) xs[k] = (k < s && a.X != nullptr) ? Xt[(int64_t)k * E + e] : 0.f;
+    for (int k = 0; k < SS; ++k) {
+      if (k < s && a.X != nullptr) {
+        if (VEC == 4) {
+          const float4 v = *reinterpret_cast<const float4*>(Xt + (int64_t)k * E + e);
+          xs[k][0] = v.x; xs[k][1] = v.y; xs[k][2] = v.z; xs[k][VEC - 1] = v.w;
+        } else {
+          xs[k][0] = Xt[(int64_t)k * E + e];
+        }
+      } else {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) xs[k][v] = 0.f;
+      }
+    }
     if (a.n_y > 0) {
-      float y;
+      float y[VEC];
       if (normed) {
-        y = 0.f;
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) y[v] = 0.f;
 #pragma unroll
         for (int k = 0; k < MAX_Y; ++k)
-          if (k < a.n_y) y += a.y[k][(int64_t)t * E + e] * yfac[k] * a.y_norm[k][e];
-        y *= 1.0f / (float)a.n_y;
+          if (k < a.n_y) {
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) y[v] += a.y[k][(int64_t)t * E + e + v] * yfac[k] * a.y_norm[k][e + v];
+          }
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) y[v] *= 1.0f / (float)a.n_y;
       } else {
-        y = a.y[0][(int64_t)t * E + e];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) y[v] = a.y[0][(int64_t)t * E + e + v];
       }
-      if (a.y_out != nullptr) a.y_out[(int64_t)t * E + e] = y;
+      if (a.y_out != nullptr) {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) a.y_out[(int64_t)t * E + e + v] = y[v];
+      }
       if (a.X == nullptr) continue;
-      float nx[MAX_STREAMS];
+      float nx[SS][VEC];
 #pragma unroll
-      for (int j = 0; j < MAX_STREAMS; ++j) {
-        if (j >= s) { nx[j] = 0.f; continue; }
-        float v = 0.f;
+      for (int j = 0; j < SS; ++j) {
 #pragma unroll
-        for (int k = 0; k < MAX_STREAMS; ++k)
-          if (k < s) v = fmaf(s_mix[k * s + j], xs[k], v);
-        nx[j] = fmaf(s_out[j], y, v);
+        for (int v = 0; v < VEC; ++v) {
+          float acc = 0.f;
+          if (j < s) {
+#pragma unroll
+            for (int k = 0; k < SS; ++k)
+              if (k < s) acc = fmaf(s_mix[k * s + j], xs[k][v], acc);
+            acc = fmaf(s_out[j], y[v], acc);
+          }
+          nx[j][v] = acc;
+        }
       }
 #pragma unroll
-      for (int j = 0; j < MAX_STREAMS; ++j)
-        if (j < s) { xs[j] = nx[j]; Xt[(int64_t)j * E + e] = nx[j]; }
+      for (int j = 0; j < SS; ++j) {
+        if (j >= s) continue;
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) xs[j][v] = nx[j][v];
+        if (VEC == 4) *reinterpret_cast<float4*>(Xt + (int64_t)j * E + e) = make_float4(nx[j][0], nx[j][1], nx[j][2], nx[j][VEC - 1]);
+        else Xt[(int64_t)j * E + e] = nx[j][0];
+      }
     }
     if (a.w_in != nullptr) {
-      float u = 0.f;
 #pragma unroll
-      for (int k = 0; k < MAX_STREAMS; ++k)
-        if (k < s) u = fmaf(s_in[k], xs[k], u);
-      urow[e] = u;
-      ss += u * u;
+      for (int v = 0; v < VEC; ++v) {
+        float u = 0.f;
+#pragma unroll
+        for (int k = 0; k < SS; ++k)
+          if (k < s) u = fmaf(s_in[k], xs[k][v], u);
+        urow[e + v] = u;
+        ss += u * u;
+      }
     }
   }
   if (a.w_in == nullptr) return;
@@ -161,18 +207,32 @@ RB_EXPORT int rb_stream_step(float* X, int T, int s, int E, const float* const* 
   }
   a.mix = mix; a.w_out = w_out; a.w_in = w_in; a.norm_w = norm_w; a.eps = eps; a.h_out = h_out; a.y_out = y_out;
   const size_t smem = w_in != nullptr ? (size_t)E * sizeof(float) : 0;
-  const int threads = E >= 1024 ? 256 : 128;
-  if (h_dtype == RB_BF16) {
-    if (smem > 48 * 1024)
-      RB_CUDA(cudaFuncSetAttribute(stream_step_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    RB_LAUNCH("stream_step_kernel", (stream_step_kernel<__nv_bfloat16>), T, threads, smem, stream, a);
-  } else if (h_dtype == RB_F32) {
-    if (smem > 48 * 1024)
-      RB_CUDA(cudaFuncSetAttribute(stream_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    RB_LAUNCH("stream_step_kernel", (stream_step_kernel<float>), T, threads, smem, stream, a);
-  } else {
-    RB_FAIL("rb_stream_step: unknown dtype %d", h_dtype);
-  }
+  bool vec = E % 4 == 0 && (uintptr_t)X % 16 == 0 && (uintptr_t)y_out % 16 == 0;
+  for (int k = 0; k < n_y; ++k) vec = vec && (uintptr_t)a.y[k] % 16 == 0 && (uintptr_t)a.y_norm[k] % 16 == 0;
+  vec = vec && (s <= 4 || s == 8);        // other numbers of streams take the kernel for any number, value by value
+  const int per = vec ? 4 : 1;
+  int threads = 64;
+  while (threads < 256 && threads * per < E) threads *= 2;
+#define LAUNCH(TO, S, V)                                                                                             \
+  do {                                                                                                               \
+    if (smem > 48 * 1024)                                                                                            \
+      RB_CUDA(cudaFuncSetAttribute(stream_step_kernel<TO, S, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    RB_LAUNCH("stream_step_kernel", (stream_step_kernel<TO, S, V>), T, threads, smem, stream, a);                    \
+  } while (0)
+#define BY_STREAMS(TO)                                                                                               \
+  do {                                                                                                               \
+    if (vec && s == 1) LAUNCH(TO, 1, 4);                                                                             \
+    else if (vec && s == 2) LAUNCH(TO, 2, 4);                                                                        \
+    else if (vec && s == 3) LAUNCH(TO, 3, 4);                                                                        \
+    else if (vec && s == 4) LAUNCH(TO, 4, 4);                                                                        \
+    else if (vec && s == 8) LAUNCH(TO, 8, 4);                                                                        \
+    else LAUNCH(TO, 0, 1);                                                                                           \
+  } while (0)
+  if (h_dtype == RB_BF16) BY_STREAMS(__nv_bfloat16);
+  else if (h_dtype == RB_F32) BY_STREAMS(float);
+  else RB_FAIL("rb_stream_step: unknown dtype %d", h_dtype);
+#undef BY_STREAMS
+#undef LAUNCH
   RB_CHECK_LAUNCH("rb_stream_step");
   return 0;
 }

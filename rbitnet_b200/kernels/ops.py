@@ -583,7 +583,7 @@ class CudaOps:
         self.lib.call("rb_gated_scan", _ptr(out), self.code, _ptr(u), _ptr(gates), _ptr(f["ra.b"]), _ptr(f["ri.b"]),
                       _ptr(f["lam"]), float(p.decay_scale), _ptr(proj), proj.stride(0), F32, 0, W, _ptr(f["x.b"]),
                       _ptr(f["y.b"]), _ptr(state["S"]), _ptr(tail), _ptr(first), _ptr(count), _ptr(meta.tok_slot), n_seq,
-                      W, Wb, K, self._stream())
+                      T, W, Wb, K, self._stream(), launches=1 if first is None else 2)
         return out
 
     def matrix_memory(self, proj: torch.Tensor, p, state, meta) -> torch.Tensor:

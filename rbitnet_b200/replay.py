@@ -36,6 +36,10 @@ from pathlib import Path
 from typing import Dict, Iterable, Iterator, List
 
 
+#: live requests whose partly used last page the cache has room for, beyond --max-tokens
+_ROOM_FOR_REQUESTS = 64
+
+
 # ------------------------------------------------------------------ schedules
 def schedule_whole(reqs: Dict[str, List[int]]) -> List[dict]:
     return [{"step": i, "entries": [{"id": r, "tokens": list(t), "want": list(range(len(t)))}], "end": [r]}
@@ -144,7 +148,7 @@ def main(argv=None, stdin=None, stdout=None, ops=None) -> int:
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     ap.add_argument("--out", required=True, help="folder for <step>.f32 and manifest.json")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to 64")
+                    help="most tokens live requests hold at any time (padding not counted)")
     ap.add_argument("--mode", choices=["stdin", "whole", "tail32", "batches"], default="stdin",
                     help="stdin: step lines from standard input; else a schedule made from --requests")
     ap.add_argument("--requests", help="file of requests for the schedule modes")
@@ -167,7 +171,10 @@ def main(argv=None, stdin=None, stdout=None, ops=None) -> int:
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
     kw = {"ops": ops} if ops is not None else {}
-    engine = Engine.load_path(args.model, dtype=args.dtype, max_tokens=args.max_tokens, verbose=True, **kw)
+    # every live request may leave its last page partly used: room for that beside the tokens themselves
+    from .cache import PAGE_SIZE
+    engine = Engine.load_path(args.model, dtype=args.dtype, max_tokens=args.max_tokens + PAGE_SIZE * _ROOM_FOR_REQUESTS,
+                              verbose=True, **kw)
     manifest = run_steps(engine, steps, out_dir, stdout)
     manifest.update(mode=args.mode, dtype=args.dtype, model=str(args.model))
     tmp = out_dir / ".manifest.json.tmp"
