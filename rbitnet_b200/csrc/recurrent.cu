@@ -173,59 +173,86 @@ __global__ void __launch_bounds__(SCAN_CH * SCAN_CHUNKS) gated_scan_chunked_kern
 // row d of the memory (R rows at most), so a token costs it 2 R multiply-adds and the sums over d are
 // finished with log2(P) shuffles.  Rows of the projections: [q (H D) | k (H D) | v (H Dv) | ... ], gate
 // pre-activations at columns i_off + h and f_off + h.  Tokens are staged TT at a time in shared memory.
-constexpr int MM_THREADS = 128;
 constexpr int MM_TT = 16;
 
 __device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* src) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async_f32x4(float* smem_dst, const float* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// The projections are float32 rows.  A tile of TT tokens (q, k, the block's value columns, the two gate
-// pre-activations) is copied into one of two shared buffers with cp.async while the tile before it is
-// worked on, so the loop over tokens never waits for global memory.
-template <int R>
-__global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(
+// One block per (run, head, tile of value columns); blockDim / P columns per block.  A thread owns one value
+// column j and the rows d = part + P r (r < R) of the memory, so a token costs it 2 R multiply-adds for the
+// memory and as many for the sums over d, which P lanes finish with shuffles, a whole tile of tokens at once.
+// The projections are float32 rows [q (H D) | k (H D) | v (H Dv) | ...], gate pre-activations at columns
+// i_off + h and f_off + h.  A tile of TT tokens is copied into one of two shared buffers with cp.async while the
+// tile before it is worked on (16 bytes at a time where the rows allow, vec4 != 0); rows of k and q are P R long
+// in shared memory, zeros behind D, so the loop over d needs no test and its addresses are constants.
+template <int P, int R>
+__global__ void __launch_bounds__(128) matrix_memory_kernel(
     float* __restrict__ o_out, const float* __restrict__ proj, int64_t ld, int q_off, int k_off, int v_off, int i_off,
     int f_off, const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap, float q_scale,
     float floor_add, float* __restrict__ C_state, float* __restrict__ n_state, float* __restrict__ m_state,
     const int* __restrict__ seq_first, const int* __restrict__ seq_count, const int* __restrict__ tok_slot, int H, int D,
-    int Dv, int P) {
+    int Dv, int vec4) {
   rb_pdl_launch_dependents();
   extern __shared__ __align__(16) float sm[];
-  const int cols = MM_THREADS / P;
-  const int tile_floats = MM_TT * (2 * D + cols + 2);
+  constexpr int Dp = P * R;
+  const int threads = blockDim.x;
+  const int cols = threads / P;
+  const int cols4 = (cols + 3) & ~3;
+  const int tile_floats = MM_TT * (2 * Dp + cols4 + 4);
   const int h = blockIdx.y;
   const int col = threadIdx.x / P, part = threadIdx.x % P;
   const int j = blockIdx.z * cols + col;
   const bool live = j < Dv;
   const float ib = i_bias != nullptr ? i_bias[h] : 0.f, fb = f_bias != nullptr ? f_bias[h] : 0.f;
+  float* s_dec = sm + 2 * tile_floats;           // [TT][3]: decay of the memory, weight of the new pair, e^(-m)
+  float* s_m = s_dec + 3 * MM_TT;                // the running maximum at the end of the tile before
+  // zeros behind D in both buffers, once (the copies never write there)
+  for (int e = threadIdx.x; e < 2 * 2 * MM_TT * Dp; e += threads) {
+    const int b = e / (2 * MM_TT * Dp), r = e % (2 * MM_TT * Dp);
+    if (r % Dp >= D) sm[b * tile_floats + r] = 0.f;
+  }
   rb_pdl_wait();
   const int first = seq_first != nullptr ? seq_first[blockIdx.x] : blockIdx.x;
   const int n = seq_count != nullptr ? seq_count[blockIdx.x] : 1;
   const int slot = tok_slot[first];
 
   auto stage = [&](int t0, int buf) {
-    float* s_q = sm + buf * tile_floats;
-    float* s_k = s_q + MM_TT * D;
-    float* s_v = s_k + MM_TT * D;
-    float* s_g = s_v + MM_TT * cols;            // [TT][2]: input gate, forget gate (pre-activations)
+    float* s_q = sm + buf * tile_floats;         // [TT][Dp]
+    float* s_k = s_q + MM_TT * Dp;               // [TT][Dp]
+    float* s_v = s_k + MM_TT * Dp;               // [TT][cols4]
+    float* s_g = s_v + MM_TT * cols4;            // [TT][2]: input gate, forget gate (pre-activations)
     const int nt = min(MM_TT, n - t0);
-    for (int e = threadIdx.x; e < nt * D; e += MM_THREADS) {
-      const int tt = e / D, d = e % D;
-      const float* row = proj + (int64_t)(first + t0 + tt) * ld;
-      cp_async_f32(s_q + e, row + q_off + h * D + d);
-      cp_async_f32(s_k + e, row + k_off + h * D + d);
+    if (vec4) {
+      const int D4 = D >> 2;
+      for (int e = threadIdx.x; e < nt * D4; e += threads) {
+        const int tt = e / D4, d = (e - tt * D4) << 2;
+        const float* row = proj + (int64_t)(first + t0 + tt) * ld + h * D + d;
+        cp_async_f32x4(s_q + tt * Dp + d, row + q_off);
+        cp_async_f32x4(s_k + tt * Dp + d, row + k_off);
+      }
+    } else {
+      for (int e = threadIdx.x; e < nt * D; e += threads) {
+        const int tt = e / D, d = e - tt * D;
+        const float* row = proj + (int64_t)(first + t0 + tt) * ld + h * D + d;
+        cp_async_f32(s_q + tt * Dp + d, row + q_off);
+        cp_async_f32(s_k + tt * Dp + d, row + k_off);
+      }
     }
-    for (int e = threadIdx.x; e < nt * cols; e += MM_THREADS) {
-      const int tt = e / cols, cc = e % cols;
+    for (int e = threadIdx.x; e < nt * cols; e += threads) {
+      const int tt = e / cols, cc = e - tt * cols;
       const int jj = blockIdx.z * cols + cc;
-      if (jj < Dv) cp_async_f32(s_v + e, proj + (int64_t)(first + t0 + tt) * ld + v_off + h * Dv + jj);
-      else s_v[e] = 0.f;
+      if (jj < Dv) cp_async_f32(s_v + tt * cols4 + cc, proj + (int64_t)(first + t0 + tt) * ld + v_off + h * Dv + jj);
+      else s_v[tt * cols4 + cc] = 0.f;
     }
-    for (int tt = threadIdx.x; tt < nt; tt += MM_THREADS) {
+    for (int tt = threadIdx.x; tt < nt; tt += threads) {
       const float* row = proj + (int64_t)(first + t0 + tt) * ld;
       cp_async_f32(s_g + 2 * tt, row + i_off + h);
       cp_async_f32(s_g + 2 * tt + 1, row + f_off + h);
@@ -243,7 +270,7 @@ __global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(
     Cr[r] = (live && d < D) ? Cs[(int64_t)d * Dv + j] : 0.f;
     nr[r] = d < D ? ns[d] : 0.f;
   }
-  float m = m_state[(int64_t)slot * H + h];
+  if (threadIdx.x == 0) *s_m = m_state[(int64_t)slot * H + h];
   int buf = 0;
   for (int t0 = 0; t0 < n; t0 += MM_TT, buf ^= 1) {
     const int nt = min(MM_TT, n - t0);
@@ -254,42 +281,85 @@ __global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(
       cp_async_wait<0>();
     }
     __syncthreads();
-    float* s_q = sm + buf * tile_floats;
-    float* s_k = s_q + MM_TT * D;
-    float* s_v = s_k + MM_TT * D;
-    float* s_g = s_v + MM_TT * cols;
-    if (threadIdx.x < nt) {
-      const float ip = s_g[2 * threadIdx.x] + ib, fp = s_g[2 * threadIdx.x + 1] + fb;
-      const float fc = cap * tanhf(fp / cap);
-      s_g[2 * threadIdx.x] = cap * tanhf(ip / cap);
-      s_g[2 * threadIdx.x + 1] = fminf(fc, 0.f) - log1pf(expf(-fabsf(fc)));       // log sigmoid
+    const float* s_q = sm + buf * tile_floats;
+    const float* s_k = s_q + MM_TT * Dp;
+    const float* s_v = s_k + MM_TT * Dp;
+    const float* s_g = s_v + MM_TT * cols4;
+    // The tile's gates at once, by the first warp (lane = token).  m_t = max(f_t + m_(t-1), i_t) unrolls to
+    // m_t = F_t + max(m_0, max_(s<=t)(i_s - F_s)) with F_t the sum of the tile's log forget gates up to t: a prefix
+    // sum and a prefix maximum.  What the loop over tokens needs of them (e^(f + m_(t-1) - m_t), e^(i - m_t), e^(-m_t))
+    // is left in shared memory, so that loop holds no exponential.
+    if (threadIdx.x < 32) {
+      const int tt = threadIdx.x;
+      const bool on = tt < nt;
+      float ig = -INFINITY, fg = 0.f;
+      if (on) {
+        const float ip = s_g[2 * tt] + ib, fp = s_g[2 * tt + 1] + fb;
+        const float fc = cap * tanhf(fp / cap);
+        ig = cap * tanhf(ip / cap);
+        fg = fminf(fc, 0.f) - log1pf(expf(-fabsf(fc)));       // log sigmoid
+      }
+      float F = fg;
+#pragma unroll
+      for (int o = 1; o < MM_TT; o <<= 1) {
+        const float v = __shfl_up_sync(0xffffffffu, F, o);
+        if (tt >= o) F += v;
+      }
+      float G = ig - F;
+#pragma unroll
+      for (int o = 1; o < MM_TT; o <<= 1) {
+        const float v = __shfl_up_sync(0xffffffffu, G, o);
+        if (tt >= o) G = fmaxf(G, v);
+      }
+      const float m0 = *s_m;
+      const float mt = F + fmaxf(m0, G);
+      float mp = __shfl_up_sync(0xffffffffu, mt, 1);
+      if (tt == 0) mp = m0;
+      __syncwarp();
+      if (on) {
+        s_dec[3 * tt] = expf(fg + mp - mt);
+        s_dec[3 * tt + 1] = expf(ig - mt);
+        s_dec[3 * tt + 2] = expf(-mt);
+        if (tt == nt - 1) *s_m = mt;
+      }
     }
     __syncthreads();
-    for (int tt = 0; tt < nt; ++tt) {
-      const float ig = s_g[2 * tt], fg = s_g[2 * tt + 1];
-      const float m_new = fmaxf(fg + m, ig);
-      const float keep = expf(fg + m - m_new), take = expf(ig - m_new);
-      m = m_new;
-      const float tv = take * s_v[tt * cols + col];
-      float num = 0.f, nq = 0.f;
+    float num[MM_TT], nq[MM_TT];
+    const float* kp = s_k + part;
+    const float* qp = s_q + part;
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const int d = part + P * r;
-        if (d < D) {
-          const float kd = s_k[tt * D + d], qd = s_q[tt * D + d];
+    for (int tt = 0; tt < MM_TT; ++tt) {
+      num[tt] = 0.f;
+      nq[tt] = 0.f;
+      if (tt < nt) {
+        const float keep = s_dec[3 * tt], take = s_dec[3 * tt + 1];
+        const float tv = take * s_v[tt * cols4 + col];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const float kd = kp[tt * Dp + P * r], qd = qp[tt * Dp + P * r];
           Cr[r] = fmaf(keep, Cr[r], tv * kd);
           nr[r] = fmaf(keep, nr[r], take * kd);
-          num = fmaf(Cr[r], qd, num);
-          nq = fmaf(nr[r], qd, nq);
+          num[tt] = fmaf(Cr[r], qd, num[tt]);
+          nq[tt] = fmaf(nr[r], qd, nq[tt]);
         }
       }
-      for (int off = P >> 1; off > 0; off >>= 1) {
-        num += __shfl_xor_sync(0xffffffffu, num, off);
-        nq += __shfl_xor_sync(0xffffffffu, nq, off);
+    }
+    // the sums over a column's lanes and the divisions, for the whole tile at once: none waits for another
+#pragma unroll
+    for (int off = P >> 1; off > 0; off >>= 1) {
+#pragma unroll
+      for (int tt = 0; tt < MM_TT; ++tt) {
+        num[tt] += __shfl_xor_sync(0xffffffffu, num[tt], off);
+        nq[tt] += __shfl_xor_sync(0xffffffffu, nq[tt], off);
       }
-      if (live && part == 0) {
-        const float den = fmaxf(fabsf(nq * q_scale), expf(-m)) + floor_add;
-        o_out[(int64_t)(first + t0 + tt) * H * Dv + h * Dv + j] = num * q_scale / den;
+    }
+    if (live && part == 0) {
+#pragma unroll
+      for (int tt = 0; tt < MM_TT; ++tt) {
+        if (tt < nt) {
+          const float den = fmaxf(fabsf(nq[tt] * q_scale), s_dec[3 * tt + 2]) + floor_add;
+          o_out[(int64_t)(first + t0 + tt) * H * Dv + h * Dv + j] = num[tt] * q_scale / den;
+        }
       }
     }
     __syncthreads();                       // the buffer may be filled again
@@ -300,7 +370,7 @@ __global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(
     if (live && d < D) Cs[(int64_t)d * Dv + j] = Cr[r];
     if (blockIdx.z == 0 && col == 0 && d < D) ns[d] = nr[r];
   }
-  if (blockIdx.z == 0 && threadIdx.x == 0) m_state[(int64_t)slot * H + h] = m;
+  if (blockIdx.z == 0 && threadIdx.x == 0) m_state[(int64_t)slot * H + h] = *s_m;
 }
 
 // Per (token, head): o / rms(o) over the head's Dv values, times the weight, times sigmoid(gate).
@@ -391,12 +461,39 @@ RB_EXPORT int rb_gated_scan(void* out, int out_dtype, const float* u, const floa
   return 0;
 }
 
-// Lanes per value column for a memory of D rows: the smallest power of two that leaves a thread at most 16 rows
-// (32 rows beyond 512, where a warp's 32 lanes are all a column has).
+// Lanes per value column for a memory of D rows: the smallest power of two that leaves a thread at most 8 rows
+// (16 rows beyond 256, where a warp's 32 lanes are all a column has).
 RB_EXPORT int rb_matrix_memory_lanes(int D) {
   int P = 1;
-  while ((D + P - 1) / P > 16 && P < 32) P *= 2;
+  while ((D + P - 1) / P > 8 && P < 32) P *= 2;
   return P;
+}
+
+template <int P, int R>
+static int launch_matrix_memory(float* o_out, const float* proj, int64_t ld, int q_off, int k_off, int v_off, int i_off,
+                                int f_off, const float* i_bias, const float* f_bias, float cap, float q_scale,
+                                float floor_add, float* C_state, float* n_state, float* m_state, const int* seq_first,
+                                const int* seq_count, const int* tok_slot, int n_seq, int H, int D, int Dv,
+                                cudaStream_t stream) {
+  // fewer columns per block while the blocks are too few to give every SM several: the work of a token is a
+  // chain of dependent steps, and an SM hides it only behind other blocks' warps
+  int threads = 128;
+  const int64_t want = 3 * (int64_t)rb_sm_count();
+  while (threads > 32 && threads / 2 >= P && (int64_t)n_seq * H * ((Dv + threads / P - 1) / (threads / P)) < want) threads /= 2;
+  const int cols = threads / P;
+  const int cols4 = (cols + 3) & ~3;
+  const dim3 grid(n_seq, H, (Dv + cols - 1) / cols);
+  RB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "rb_matrix_memory: grid %d x %d", grid.y, grid.z);
+  const size_t smem = (size_t)(2 * MM_TT * (2 * P * R + cols4 + 4) + 3 * MM_TT + 4) * sizeof(float);
+  const int vec4 = (D % 4 == 0 && ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && (uintptr_t)proj % 16 == 0) ? 1 : 0;
+  static RbOncePerDevice once;
+  if (smem > 48 * 1024 && once.first())
+    RB_CUDA(cudaFuncSetAttribute(matrix_memory_kernel<P, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+  RB_LAUNCH("matrix_memory_kernel", (matrix_memory_kernel<P, R>), grid, threads, smem, stream, o_out, proj, ld, q_off, k_off,
+            v_off, i_off, f_off, i_bias, f_bias, cap, q_scale, floor_add, C_state, n_state, m_state, seq_first, seq_count,
+            tok_slot, H, D, Dv, vec4);
+  RB_CHECK_LAUNCH("rb_matrix_memory");
+  return 0;
 }
 
 RB_EXPORT int rb_matrix_memory(float* o_out, const void* proj, int64_t ld, int proj_dtype, int q_off, int k_off, int v_off,
@@ -405,27 +502,26 @@ RB_EXPORT int rb_matrix_memory(float* o_out, const void* proj, int64_t ld, int p
                                const int* seq_count, const int* tok_slot, int n_seq, int H, int D, int Dv,
                                cudaStream_t stream) {
   if (n_seq == 0) return 0;
-  RB_REQUIRE(H > 0 && D > 0 && Dv > 0 && D <= 1024, "rb_matrix_memory: bad sizes H=%d D=%d Dv=%d (D up to 1024)", H, D, Dv);
+  RB_REQUIRE(H > 0 && D > 0 && Dv > 0 && D <= 512, "rb_matrix_memory: bad sizes H=%d D=%d Dv=%d (D up to 512)", H, D, Dv);
   RB_REQUIRE(cap > 0.f, "rb_matrix_memory: the gates' cap must be positive");
   RB_REQUIRE(proj_dtype == RB_F32, "rb_matrix_memory: the projections are float32 rows (found dtype %d)", proj_dtype);
   const int P = rb_matrix_memory_lanes(D);
   const int per = (D + P - 1) / P;
-  const int cols = MM_THREADS / P;
-  const dim3 grid(n_seq, H, (Dv + cols - 1) / cols);
-  RB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "rb_matrix_memory: grid %d x %d", grid.y, grid.z);
-  const size_t smem = (size_t)(2 * MM_TT * (2 * D + cols + 2)) * sizeof(float);
-#define LAUNCH(RR)                                                                                                  \
-  do {                                                                                                              \
-    if (smem > 48 * 1024)                                                                                           \
-      RB_CUDA(cudaFuncSetAttribute(matrix_memory_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    RB_LAUNCH("matrix_memory_kernel", (matrix_memory_kernel<RR>), grid, MM_THREADS, smem, stream, o_out,            \
-              (const float*)proj, ld, q_off, k_off, v_off, i_off, f_off, i_bias, f_bias, cap, q_scale, floor_add,   \
-              C_state, n_state, m_state, seq_first, seq_count, tok_slot, H, D, Dv, P);                              \
-  } while (0)
-  if (per <= 16) LAUNCH(16); else LAUNCH(32);
-#undef LAUNCH
-  RB_CHECK_LAUNCH("rb_matrix_memory");
-  return 0;
+#define GO(PP, RR)                                                                                                    \
+  return launch_matrix_memory<PP, RR>(o_out, (const float*)proj, ld, q_off, k_off, v_off, i_off, f_off, i_bias, f_bias, \
+                                      cap, q_scale, floor_add, C_state, n_state, m_state, seq_first, seq_count,       \
+                                      tok_slot, n_seq, H, D, Dv, stream)
+  switch (P) {
+    case 1: GO(1, 8);
+    case 2: GO(2, 8);
+    case 4: GO(4, 8);
+    case 8: GO(8, 8);
+    case 16: GO(16, 8);
+    default:
+      if (per <= 8) GO(32, 8);
+      GO(32, 16);
+  }
+#undef GO
 }
 
 RB_EXPORT int rb_head_norm_gate(void* out, int out_dtype, const float* o, const float* w, const void* proj, int64_t ld,
