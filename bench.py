@@ -572,6 +572,10 @@ def run_design(name, args):
             for pool in g.pools:
                 pool.normal_(0.0, 1.0)
         torch.cuda.synchronize()
+        if args.timeline:
+            if label == "safuvik":
+                print_timeline(engine, args.batch, ctx)
+            continue
         pf_ms = time_prefill(engine, args.prefill_tokens)
         ms, launches, _ = time_decode(engine, args.batch, ctx, steps, warmup)
         nbytes = decode_bytes(engine, args.batch, ctx if label == "llama" else min(ctx, 1024))
@@ -597,6 +601,8 @@ def run_design(name, args):
         out["models"][label] = rec
         del engine
         torch.cuda.empty_cache()
+    if args.timeline:
+        return 0
     print(json.dumps(out))
     for label, rec in out["models"].items():
         print(f"\n{label} {name}: prefill {rec['prefill_tokens_per_s']:.0f} tok/s ({rec['prefill_ms']:.2f} ms), decode "

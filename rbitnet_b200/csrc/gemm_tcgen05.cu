@@ -105,7 +105,20 @@ struct GemmParams {
   const float* emit_g;
   float* emit_ss;
   QkvTail qkv;        // EPI_QKV only
+  // EPI_GATED: out = g' / (1 + e^(-act_alpha g')) * (u' + act_shift), g' = min(g, act_limit), u' = clamp(u, +-act_limit)
+  // (act_limit <= 0: no limit).  1, 0, 0 is SiLU(gate) * up.
+  float act_alpha, act_limit, act_shift;
 };
+
+// The gated epilogue's value, with the hardware's exponential and reciprocal: their error (a few units of
+// float32) is far below the rounding to bfloat16 that follows.
+__device__ __forceinline__ float gated_value(const GemmParams& p, float g, float up) {
+  if (p.act_limit > 0.f) {
+    g = fminf(g, p.act_limit);
+    up = fminf(fmaxf(up, -p.act_limit), p.act_limit);
+  }
+  return __fdividef(g, 1.0f + __expf(-p.act_alpha * g)) * (up + p.act_shift);
+}
 
 // What one pass of a CTA's three roles covers: k blocks kb_begin .. kb_begin + nkb - 1 of the tile
 // at (n0, t0).  With shared ranges a tile's K may be covered by `parts` teams, of which this is
@@ -439,7 +452,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               const float g = low ? mine : got, up = low ? got : mine;
               // silu(g) * up = g * up / (1 + e^-g), with the hardware's exponential and reciprocal: their
               // error (a few units of float32) is far below the rounding to bfloat16 that follows
-              store_out<OutT>(dst + j * OUT_COLS, __fdividef(g, 1.0f + __expf(-g)) * up);
+              store_out<OutT>(dst + j * OUT_COLS, gated_value(p, g, up));
             }
           } else {
 #pragma unroll
@@ -497,7 +510,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               const float got = __shfl_xor_sync(0xffffffffu, send, 16);
               const float rr = normed ? norm_r[t0 + c + j + (low ? 0 : 1)] : 1.0f;       // my token's pending norm
               const float g = (low ? mine : got) * rr, up = (low ? got : mine) * rr;
-              const float v = __fdividef(g, 1.0f + __expf(-g)) * up;
+              const float v = gated_value(p, g, up);
               if (j + (low ? 0 : 1) < f_left) store_out<OutT>(dst + (int64_t)j * p.ldc, v);
             }
           } else {
@@ -653,7 +666,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               const float up = __shfl_xor_sync(0xffffffffu, v, 16);
               const int f = (n0 + quarter * 32) / 2 + (lane & 15);
               if (ok[h] && lane < 16 && f < p.n_features)
-                store_out<OutT>((OutT*)p.C + (int64_t)(t0 + col[h]) * p.ldc + f, __fdividef(v, 1.0f + __expf(-v)) * up);
+                store_out<OutT>((OutT*)p.C + (int64_t)(t0 + col[h]) * p.ldc + f, gated_value(p, v, up));
               continue;
             }
             float now = 0.f;
@@ -1038,7 +1051,16 @@ struct NormOptions {
   void* out_xb = nullptr; int64_t out_ld = 0; const float* out_g = nullptr; float* out_ss = nullptr;
 };
 thread_local NormOptions t_norm;
+struct GatedAct { float alpha = 1.f, limit = 0.f, shift = 0.f; };
+thread_local GatedAct t_act;
 }  // namespace
+
+// The next gated product (epilogue 3) of this thread applies g' sigmoid(alpha g') (u' + shift) with g' = min(g, limit)
+// and u' = clamp(u, -limit, limit) (limit <= 0: none) instead of SiLU(gate) * up.
+RB_EXPORT int rb_gemm_tc_gated_act(float alpha, float limit, float shift) {
+  t_act.alpha = alpha; t_act.limit = limit; t_act.shift = shift;
+  return 0;
+}
 
 // The rows of X are rows * norm weight with the norm's factor pending: ss [parts, n_tokens] float32
 // holds sums of squares of the rows (over `width` values in all).  At most 16 tokens.
@@ -1073,6 +1095,8 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
                    int token_tile, const QkvTail* tail, float alpha, cudaStream_t stream) {
   const NormOptions norm = t_norm;
   t_norm = NormOptions();
+  const GatedAct act = t_act;
+  t_act = GatedAct();
   if (n_tokens == 0 || n_out == 0) return 0;
   RB_REQUIRE(alpha == 1.0f || epilogue == EPI_STORE || epilogue == EPI_ADD, "rb_gemm_tc: alpha %g with epilogue %d", alpha, epilogue);
   RB_REQUIRE(n_tokens > 0 && n_out > 0 && K > 0, "rb_gemm_tc: bad sizes tokens=%d out=%d K=%d", n_tokens, n_out, K);
@@ -1121,6 +1145,7 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
       const int rows_main = (int)w_main * BM;
       const int64_t out_off = epilogue == EPI_GATED ? rows_main / 2 : rows_main;       // columns of C the main product fills
       const int feat_main = epilogue == EPI_GATED ? (n_features < out_off ? n_features : (int)out_off) : 0;
+      t_act = act;                 // both products of the pair apply the caller's activation
       if (gemm_tc(C, ldc, c_dtype, X, ldx, n_tokens, W, ldw, rows_main, rows_main, K, epilogue, feat_main, 1, bn, nullptr,
                   alpha, stream) != 0)
         return -1;
@@ -1128,6 +1153,7 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
       char* c_tail = (char*)C + out_off * out_elem;
       const char* w_rest = (const char*)W + (int64_t)rows_main * ldw * 2;
       const int per = (nkb + parts - 1) / parts;
+      t_act = act;
       return gemm_tc(c_tail, ldc, c_dtype, X, ldx, n_tokens, w_rest, ldw, w_rows - rows_main, n_out - rows_main, K, epilogue,
                      epilogue == EPI_GATED ? n_features - (int)out_off : 0, (nkb + per - 1) / per, 64, nullptr, alpha, stream);
     }
@@ -1150,6 +1176,10 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
   p.n_t_tiles = n_t_tiles; p.splits = splits; p.n_items = (int)items;
   p.cluster = splits > 1 ? 1 : 0;
   p.alpha = alpha;
+  p.act_alpha = 1.f; p.act_limit = 0.f; p.act_shift = 0.f;
+  if (epilogue == EPI_GATED) {
+    p.act_alpha = act.alpha; p.act_limit = act.limit; p.act_shift = act.shift;
+  }
   p.norm_ss = norm.in_ss; p.norm_parts = norm.in_parts; p.norm_width = norm.in_width; p.norm_eps = norm.in_eps;
   RB_REQUIRE(norm.in_ss == nullptr || (bn <= 16 && n_tokens <= 16),
              "rb_gemm_tc: a pending norm with %d tokens in tiles of %d (at most 16 tokens)", n_tokens, bn);

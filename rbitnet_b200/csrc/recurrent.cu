@@ -186,6 +186,7 @@ __device__ __forceinline__ void cp_async_f32x4(float* smem_dst, const float* src
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// The memory of a (slot, head) is kept as [value column][row] (the kernel's own layout; nobody else reads it).
 // One block per (run, head, tile of value columns); blockDim / P columns per block.  A thread owns one value
 // column j and the rows d = part + P r (r < R) of the memory, so a token costs it 2 R multiply-adds for the
 // memory and as many for the sums over d, which P lanes finish with shuffles, a whole tile of tokens at once.
@@ -215,9 +216,11 @@ __global__ void __launch_bounds__(128) matrix_memory_kernel(
   float* s_dec = sm + 2 * tile_floats;           // [TT][3]: decay of the memory, weight of the new pair, e^(-m)
   float* s_m = s_dec + 3 * MM_TT;                // the running maximum at the end of the tile before
   // zeros behind D in both buffers, once (the copies never write there)
-  for (int e = threadIdx.x; e < 2 * 2 * MM_TT * Dp; e += threads) {
-    const int b = e / (2 * MM_TT * Dp), r = e % (2 * MM_TT * Dp);
-    if (r % Dp >= D) sm[b * tile_floats + r] = 0.f;
+  if (D < Dp) {
+    for (int e = threadIdx.x; e < 2 * 2 * MM_TT * Dp; e += threads) {
+      const int b = e / (2 * MM_TT * Dp), r = e % (2 * MM_TT * Dp);
+      if (r % Dp >= D) sm[b * tile_floats + r] = 0.f;
+    }
   }
   rb_pdl_wait();
   const int first = seq_first != nullptr ? seq_first[blockIdx.x] : blockIdx.x;
@@ -267,7 +270,7 @@ __global__ void __launch_bounds__(128) matrix_memory_kernel(
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     const int d = part + P * r;
-    Cr[r] = (live && d < D) ? Cs[(int64_t)d * Dv + j] : 0.f;
+    Cr[r] = (live && d < D) ? Cs[(int64_t)j * D + d] : 0.f;      // kept [value column][row]: a column's lanes read neighbours
     nr[r] = d < D ? ns[d] : 0.f;
   }
   if (threadIdx.x == 0) *s_m = m_state[(int64_t)slot * H + h];
@@ -367,7 +370,7 @@ __global__ void __launch_bounds__(128) matrix_memory_kernel(
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     const int d = part + P * r;
-    if (live && d < D) Cs[(int64_t)d * Dv + j] = Cr[r];
+    if (live && d < D) Cs[(int64_t)j * D + d] = Cr[r];
     if (blockIdx.z == 0 && col == 0 && d < D) ns[d] = nr[r];
   }
   if (blockIdx.z == 0 && threadIdx.x == 0) m_state[(int64_t)slot * H + h] = *s_m;

@@ -83,19 +83,36 @@ class Model:
         return cache_needs, reads, state_needs
 
     def weight_bytes(self) -> int:
-        seen, total = set(), 0
+        """Bytes of every matrix a step multiplies by (prepared weights of all parts, parts inside parts
+        included, and float32 matrices a part keeps for itself; vectors and the embedding table are left out)."""
+        from ..parts.base import Part
+        seen, total, visited = set(), 0, set()
+
         def add(t):
             nonlocal total
-            if t is not None and t.data_ptr() not in seen:
+            if isinstance(t, torch.Tensor) and t.dim() >= 2 and t.data_ptr() not in seen:
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()
+
+        def walk(obj, depth=0):
+            if id(obj) in visited or depth > 4:
+                return
+            visited.add(id(obj))
+            if isinstance(obj, torch.Tensor):
+                add(obj)
+            elif isinstance(obj, dict):
+                for v in obj.values():
+                    walk(v, depth + 1)
+            elif isinstance(obj, Part):
+                for v in vars(obj).values():
+                    walk(v, depth + 1)
+            else:
+                w = getattr(obj, "w", None)
+                if isinstance(w, torch.Tensor):
+                    add(w)
         add(self.head.w)
         for b in self.blocks:
-            for part in b.parts().values():
-                for v in vars(part).values():
-                    w = getattr(v, "w", None)
-                    if isinstance(w, torch.Tensor):
-                        add(w)
+            walk(b.parts())
         return total
 
     def forward(self, ctx) -> Optional[torch.Tensor]:

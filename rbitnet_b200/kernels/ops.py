@@ -120,6 +120,8 @@ class CudaOps:
         self.fold_norms_up_to = 16
         #: what lies between two sublayers of a block over several residual streams is one kernel
         self.fuse_streams = True
+        #: a limited gated activation is applied in the tensor-core product's epilogue (else by a kernel of its own)
+        self.fuse_gated_act = True
         #: tensor-core products of more than 256 tokens may share a weight tile's inner dimension
         #: between teams of CTAs (needs the workspace; tiles are taken in turn without it)
         _give_gemm_workspace(self.lib, self.device)
@@ -288,6 +290,16 @@ class CudaOps:
     def gated_linear(self, x: torch.Tensor, weight: GateUpWeight, act=None) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) -> [T, inner] in the compute dtype.  ``act`` = (alpha, limit, shift):
         g' sigmoid(alpha g') (u' + shift) with g' = min(g, limit), u' = clamp(u, -limit, limit) instead."""
+        if act is not None and weight.block == 16 and not isinstance(x, NormedRows) and self.fuse_gated_act \
+                and self._tensor_core_ok(x, weight.w):
+            # the tensor-core gated product with the limited activation in its epilogue
+            T, rows = x.shape[0], weight.w.shape[0]
+            out = torch.empty((T, weight.inner), dtype=self.dtype, device=self.device)
+            self.lib.call("rb_gemm_tc_gated_act", float(act[0]), float(act[1]), float(act[2]), launches=0)
+            self.lib.call("rb_gemm_tc", _ptr(out), out.stride(0), self.code, _ptr(x), x.stride(0), T,
+                          _ptr(weight.w), weight.w.stride(0), rows, rows, weight.n_in, 3, weight.inner, 1, 0,
+                          1.0, self._stream())
+            return out
         if act is not None:
             if isinstance(x, NormedRows):
                 x = self.normed(x)

@@ -254,13 +254,16 @@ def test_gated_recurrence_kernels(ops32, W, B, K):
         assert rel_err(torch.cat(outs).cpu(), want) <= 2e-4, cuts
 
 
+@pytest.mark.parametrize("T,fused", [(19, True), (19, False), (300, True), (700, True)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_limited_gated_activation(dtype):
+def test_limited_gated_activation(dtype, T, fused):
+    """In the tensor-core product's epilogue (bfloat16: tiles of 16 to 256 tokens) and as a kernel of its own."""
     from rbitnet_b200.kernels.ops import CudaOps
     from rbitnet_b200.parts.feed_forward import GatedDense
     ops = CudaOps(dtype)
+    ops.fuse_gated_act = fused
     g = torch.Generator().manual_seed(5)
-    E, F, T = 64, 88, 19
+    E, F = 64, 88
     part = GatedDense(E, F, "swish_limited", limit=0.8)
     w = {k: (torch.randn(*shape, generator=g) * 0.4).to(torch.bfloat16).double() for k, (shape, _) in part.weight_shapes().items()}
     part.bind({k: v.float().cuda() for k, v in w.items()}, ops)
