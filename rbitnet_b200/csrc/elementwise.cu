@@ -539,9 +539,13 @@ __global__ void __launch_bounds__(256) norm_rotate_append_kernel(
     int rot_dim, int interleaved, int write_kv) {
   rb_pdl_launch_dependents();
   __shared__ float scratch[33];
+  extern __shared__ float s_sincos[];              // rot_dim/2 sines, then as many cosines, of this token's position
   const int t = blockIdx.x;
   const int Dc = cache.head_dim, Kh = cache.n_kv_heads;
   const int pos = tok_pos[t], slot = tok_slot[t];
+  // once per token: the float64 angle is the costly part, and every head turns by the same angles
+  for (int i = threadIdx.x; i < rot_dim / 2; i += blockDim.x)
+    rb_angle_sincos(pos, freq[i], magnitude, &s_sincos[i], &s_sincos[rot_dim / 2 + i]);
   rb_pdl_wait();
   const T* row = proj + (int64_t)t * ld;
   float rq = 1.f, rk = 1.f;
@@ -559,6 +563,7 @@ __global__ void __launch_bounds__(256) norm_rotate_append_kernel(
   }
   const int n_rot_heads = H + (write_kv ? Kh : 0);
   const int rhalf = rot_dim / 2;
+  __syncthreads();                                 // the table is complete (also without a norm's sums before)
   T* kdst = (T*)cache.k;
   T* vdst = (T*)cache.v;
   // one output value per thread and turn: a q or k head's value (normed, turned or passed), or padding
@@ -579,8 +584,7 @@ __global__ void __launch_bounds__(256) norm_rotate_append_kernel(
       bool first;
       if (interleaved) { pair = e >> 1; first = (e & 1) == 0; other = first ? e + 1 : e - 1; }
       else { first = e < rhalf; pair = first ? e : e - rhalf; other = first ? e + rhalf : e - rhalf; }
-      float sn, cs;
-      rb_angle_sincos(pos, freq[pair], magnitude, &sn, &cs);
+      const float sn = s_sincos[pair], cs = s_sincos[rhalf + pair];
       const float me = value(e), ot = value(other);
       y = first ? me * cs - ot * sn : me * cs + ot * sn;
     }
@@ -608,9 +612,9 @@ RB_EXPORT int rb_norm_rotate_append(void* q_out, const void* proj, int64_t ld, i
              "rb_norm_rotate_append: the rotated prefix %d must be even and at most the head size %d", rot_dim, D);
   RbPagedLayer c{cache_k, cache_v, page_table, max_pages, page_size, Kh, Dc};
   if (dtype == RB_F32)
-    RB_LAUNCH("norm_rotate_append_kernel", (norm_rotate_append_kernel<float>), T, 256, 0, stream, (float*)q_out, (const float*)proj, ld, q_norm_w, k_norm_w, eps, freq, magnitude, tok_pos, tok_slot, c, H, D, Dv, rot_dim, interleaved, write_kv);
+    RB_LAUNCH("norm_rotate_append_kernel", (norm_rotate_append_kernel<float>), T, 256, (size_t)rot_dim * sizeof(float), stream, (float*)q_out, (const float*)proj, ld, q_norm_w, k_norm_w, eps, freq, magnitude, tok_pos, tok_slot, c, H, D, Dv, rot_dim, interleaved, write_kv);
   else if (dtype == RB_BF16)
-    RB_LAUNCH("norm_rotate_append_kernel", (norm_rotate_append_kernel<__nv_bfloat16>), T, 256, 0, stream, (__nv_bfloat16*)q_out, (const __nv_bfloat16*)proj, ld, q_norm_w, k_norm_w, eps, freq, magnitude, tok_pos, tok_slot, c, H, D, Dv, rot_dim, interleaved, write_kv);
+    RB_LAUNCH("norm_rotate_append_kernel", (norm_rotate_append_kernel<__nv_bfloat16>), T, 256, (size_t)rot_dim * sizeof(float), stream, (__nv_bfloat16*)q_out, (const __nv_bfloat16*)proj, ld, q_norm_w, k_norm_w, eps, freq, magnitude, tok_pos, tok_slot, c, H, D, Dv, rot_dim, interleaved, write_kv);
   else
     RB_FAIL("rb_norm_rotate_append: unknown dtype %d", dtype);
   RB_CHECK_LAUNCH("rb_norm_rotate_append");

@@ -22,19 +22,21 @@ __device__ __forceinline__ float gelu_tanh_(float z) {
 
 // ---------------------------------------------------------------- causal convolution
 // x: rows [T, ldx] of the projections' dtype, the convolved channels at column x_off; the bias x_bias
-// is added to every input before the taps.  tail: [n_slots, K-1, C] float32, the last K-1 inputs
-// (with their bias) of the slot's sequence before this step; zeros at the start of a sequence.
-// tok_first: row of the first token of the row's run (null: every row is its own run).
+// is added to every input before the taps.  tail: [n_slots, K, C] float32, a ring by position: the input
+// (with its bias) of position q of the slot's sequence is kept at row q mod K, so that writing a position
+// never touches one of the K-1 positions before it, which the same step may still be reading; zeros at
+// the start of a sequence.  tok_first: row of the first token of the row's run (null: every row is its own run).
 template <typename TI>
 __global__ void conv_causal_kernel(float* __restrict__ u, const TI* __restrict__ x, int64_t ldx, int x_off,
                                    const float* __restrict__ x_bias, const float* __restrict__ taps,
                                    const float* __restrict__ conv_bias, const float* __restrict__ tail,
-                                   const int* __restrict__ tok_first, const int* __restrict__ tok_slot, int C, int K) {
+                                   const int* __restrict__ tok_first, const int* __restrict__ tok_slot,
+                                   const int* __restrict__ tok_pos, int C, int K) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
   const int t = blockIdx.x;
   const int first = tok_first != nullptr ? tok_first[t] : t;
-  const int slot = tok_slot[t];
+  const int slot = tok_slot[t], pos = tok_pos[t];
   const int j = t - first;                      // rows of this run before this one
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
     float acc = conv_bias != nullptr ? conv_bias[c] : 0.f;
@@ -42,7 +44,8 @@ __global__ void conv_causal_kernel(float* __restrict__ u, const TI* __restrict__
     for (int d = 0; d < K; ++d) {               // d tokens back
       float v;
       if (d <= j) v = rb_to_float<TI>(x[(int64_t)(t - d) * ldx + x_off + c]) + xb;
-      else v = tail[((int64_t)slot * (K - 1) + (K - 1 + j - d)) * C + c];
+      else if (pos - d < 0) v = 0.f;
+      else v = tail[((int64_t)slot * K + (pos - d) % K) * C + c];
       acc = fmaf(taps[(int64_t)c * K + (K - 1 - d)], v, acc);
     }
     u[(int64_t)t * C + c] = acc;
@@ -58,7 +61,7 @@ __global__ void __launch_bounds__(64) gated_scan_kernel(
     const float* __restrict__ gate_i_bias, const float* __restrict__ lam, float decay_scale, const TI* __restrict__ xy,
     int64_t ldxy, int x_off, int y_off, const float* __restrict__ x_bias, const float* __restrict__ y_bias,
     float* __restrict__ state, float* __restrict__ tail, const int* __restrict__ seq_first,
-    const int* __restrict__ seq_count, const int* __restrict__ tok_slot, int W, int Wb, int K) {
+    const int* __restrict__ seq_count, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, int W, int Wb, int K) {
   rb_pdl_launch_dependents();
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= W) return;
@@ -82,14 +85,14 @@ __global__ void __launch_bounds__(64) gated_scan_kernel(
     out[(int64_t)t * W + c] = rb_from_float<TO>(S * y);
   }
   state[(int64_t)slot * W + c] = S;
-  // the last K-1 inputs of the sequence, oldest first
-  float keep[8];
-  for (int k = 0; k < K - 1; ++k) {
-    const int back = K - 2 - k;                 // tokens before the run's last one
-    keep[k] = back < n ? rb_to_float<TI>(xy[(int64_t)(first + n - 1 - back) * ldxy + x_off + c]) + xb
-                       : tail[((int64_t)slot * (K - 1) + (k + n)) * W + c];
+  // the run's last inputs go to their rows of the ring
+  if (K > 1) {
+    const int pos0 = tok_pos[first];
+    for (int back = 0; back < K - 1 && back < n; ++back) {
+      const int q = pos0 + n - 1 - back;
+      tail[((int64_t)slot * K + q % K) * W + c] = rb_to_float<TI>(xy[(int64_t)(first + n - 1 - back) * ldxy + x_off + c]) + xb;
+    }
   }
-  for (int k = 0; k < K - 1; ++k) tail[((int64_t)slot * (K - 1) + k) * W + c] = keep[k];
 }
 
 // ---- long runs: the gates become decays and drives in one pass over all rows, then a scan in chunks of time
@@ -121,7 +124,8 @@ template <typename TI, typename TO>
 __global__ void __launch_bounds__(SCAN_CH * SCAN_CHUNKS) gated_scan_chunked_kernel(
     TO* __restrict__ out, const float* __restrict__ ab, const TI* __restrict__ xy, int64_t ldxy, int x_off, int y_off,
     const float* __restrict__ x_bias, const float* __restrict__ y_bias, float* __restrict__ state, float* __restrict__ tail,
-    const int* __restrict__ seq_first, const int* __restrict__ seq_count, const int* __restrict__ tok_slot, int W, int Wb, int K) {
+    const int* __restrict__ seq_first, const int* __restrict__ seq_count, const int* __restrict__ tok_slot,
+    const int* __restrict__ tok_pos, int W, int Wb, int K) {
   rb_pdl_launch_dependents();
   __shared__ float sA[SCAN_CHUNKS][SCAN_CH], sB[SCAN_CHUNKS][SCAN_CH];
   const int lane = threadIdx.x & 31, chunk = threadIdx.x >> 5;
@@ -157,14 +161,82 @@ __global__ void __launch_bounds__(SCAN_CH * SCAN_CHUNKS) gated_scan_chunked_kern
   }
   if (!live) return;
   if (chunk == SCAN_CHUNKS - 1) state[(int64_t)slot * W + cc] = S;       // the last chunk ends where the run ends
-  if (chunk == 0) {
-    float keep[8];
-    for (int k = 0; k < K - 1; ++k) {
-      const int back = K - 2 - k;
-      keep[k] = back < n ? rb_to_float<TI>(xy[(int64_t)(first + n - 1 - back) * ldxy + x_off + cc]) + xb
-                         : tail[((int64_t)slot * (K - 1) + (k + n)) * W + cc];
+  if (chunk == 0 && K > 1) {
+    const int pos0 = tok_pos[first];
+    for (int back = 0; back < K - 1 && back < n; ++back) {
+      const int q = pos0 + n - 1 - back;
+      tail[((int64_t)slot * K + q % K) * W + cc] = rb_to_float<TI>(xy[(int64_t)(first + n - 1 - back) * ldxy + x_off + cc]) + xb;
     }
-    for (int k = 0; k < K - 1; ++k) tail[((int64_t)slot * (K - 1) + k) * W + cc] = keep[k];
+  }
+}
+
+// ---- a few rows, each its own sequence (a decode step): convolution, gates, recurrence and output in one kernel
+// One block per (block of the gates' matrices, 32 of its channels).  It convolves all Wb channels of the block for every
+// row (the gates of a channel read them all), its warps take the 64 rows of the two gate matrices that belong to its
+// channels (a row's weights are read once, by lanes, and serve every token), and one thread per (row, channel) finishes.
+constexpr int STEP_CH = 32, STEP_MAX_ROWS = 16;
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) gated_step_kernel(
+    TO* __restrict__ out, const TI* __restrict__ xy, int64_t ldxy, int x_off, int y_off, const float* __restrict__ x_bias,
+    const float* __restrict__ y_bias, const float* __restrict__ taps, const float* __restrict__ conv_bias,
+    const float* __restrict__ w_gates, const float* __restrict__ gate_r_bias, const float* __restrict__ gate_i_bias,
+    const float* __restrict__ lam, float decay_scale, float* __restrict__ state, float* __restrict__ tail,
+    const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, int T, int W, int Wb, int K) {
+  rb_pdl_launch_dependents();
+  extern __shared__ float s_u[];                 // [T][Wb], then the gates' sums [T][2][STEP_CH]
+  float* s_g = s_u + T * Wb;
+  const int b = blockIdx.x, ch0 = blockIdx.y * STEP_CH;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  rb_pdl_wait();
+  for (int idx = threadIdx.x; idx < T * Wb; idx += blockDim.x) {
+    const int t = idx / Wb, i = idx - t * Wb, c = b * Wb + i;
+    const int slot = tok_slot[t], pos = tok_pos[t];
+    float acc = conv_bias != nullptr ? conv_bias[c] : 0.f;
+    for (int d = 0; d < K; ++d) {
+      float v;
+      if (d == 0) v = rb_to_float<TI>(xy[(int64_t)t * ldxy + x_off + c]) + (x_bias != nullptr ? x_bias[c] : 0.f);
+      else if (pos - d < 0) v = 0.f;
+      else v = tail[((int64_t)slot * K + (pos - d) % K) * W + c];
+      acc = fmaf(taps[(int64_t)c * K + (K - 1 - d)], v, acc);
+    }
+    s_u[idx] = acc;
+  }
+  __syncthreads();
+  const int n_ch = min(STEP_CH, Wb - ch0);
+  for (int rr = warp; rr < 2 * n_ch; rr += (blockDim.x >> 5)) {
+    const int which = rr / n_ch, o = ch0 + rr % n_ch;
+    const float* wrow = w_gates + ((int64_t)b * 2 * Wb + (int64_t)which * Wb + o) * Wb;
+    float acc[STEP_MAX_ROWS];
+#pragma unroll
+    for (int t = 0; t < STEP_MAX_ROWS; ++t) acc[t] = 0.f;
+    for (int i = lane; i < Wb; i += 32) {
+      const float w = wrow[i];
+#pragma unroll
+      for (int t = 0; t < STEP_MAX_ROWS; ++t)
+        if (t < T) acc[t] = fmaf(w, s_u[t * Wb + i], acc[t]);
+    }
+#pragma unroll
+    for (int t = 0; t < STEP_MAX_ROWS; ++t) {
+      if (t < T) {
+        const float v = rb_warp_sum(acc[t]);
+        if (lane == 0) s_g[(t * 2 + which) * STEP_CH + rr % n_ch] = v;
+      }
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < T * n_ch; idx += blockDim.x) {
+    const int t = idx / n_ch, ch = idx - t * n_ch, c = b * Wb + ch0 + ch;
+    const int slot = tok_slot[t], pos = tok_pos[t];
+    const float r = sigmoidf_(s_g[(t * 2) * STEP_CH + ch] + gate_r_bias[c]);
+    const float in = sigmoidf_(s_g[(t * 2 + 1) * STEP_CH + ch] + gate_i_bias[c]);
+    const float a = expf(-decay_scale * softplusf_(lam[c]) * r);
+    float S = state[(int64_t)slot * W + c];
+    S = fmaf(a, S, sqrtf(1.0f - a * a) * in * s_u[t * Wb + ch0 + ch]);
+    state[(int64_t)slot * W + c] = S;
+    const float y = gelu_tanh_(rb_to_float<TI>(xy[(int64_t)t * ldxy + y_off + c]) + (y_bias != nullptr ? y_bias[c] : 0.f));
+    out[(int64_t)t * W + c] = rb_from_float<TO>(S * y);
+    if (K > 1)
+      tail[((int64_t)slot * K + pos % K) * W + c] = rb_to_float<TI>(xy[(int64_t)t * ldxy + x_off + c]) + (x_bias != nullptr ? x_bias[c] : 0.f);
   }
 }
 
@@ -403,7 +475,7 @@ __global__ void head_norm_gate_kernel(TO* __restrict__ out, const float* __restr
 
 RB_EXPORT int rb_conv_causal(float* u, const void* x, int64_t ldx, int x_off, int x_dtype, const float* x_bias,
                              const float* taps, const float* conv_bias, const float* tail, const int* tok_first,
-                             const int* tok_slot, int T, int C, int K, cudaStream_t stream) {
+                             const int* tok_slot, const int* tok_pos, int T, int C, int K, cudaStream_t stream) {
   if (T == 0) return 0;
   RB_REQUIRE(C > 0 && K >= 1, "rb_conv_causal: bad sizes C=%d K=%d", C, K);
   const int threads = 128;
@@ -411,9 +483,9 @@ RB_EXPORT int rb_conv_causal(float* u, const void* x, int64_t ldx, int x_off, in
   if (by > 64) by = 64;
   const dim3 grid(T, by);
   if (x_dtype == RB_F32)
-    RB_LAUNCH("conv_causal_kernel", (conv_causal_kernel<float>), grid, threads, 0, stream, u, (const float*)x, ldx, x_off, x_bias, taps, conv_bias, tail, tok_first, tok_slot, C, K);
+    RB_LAUNCH("conv_causal_kernel", (conv_causal_kernel<float>), grid, threads, 0, stream, u, (const float*)x, ldx, x_off, x_bias, taps, conv_bias, tail, tok_first, tok_slot, tok_pos, C, K);
   else if (x_dtype == RB_BF16)
-    RB_LAUNCH("conv_causal_kernel", (conv_causal_kernel<__nv_bfloat16>), grid, threads, 0, stream, u, (const __nv_bfloat16*)x, ldx, x_off, x_bias, taps, conv_bias, tail, tok_first, tok_slot, C, K);
+    RB_LAUNCH("conv_causal_kernel", (conv_causal_kernel<__nv_bfloat16>), grid, threads, 0, stream, u, (const __nv_bfloat16*)x, ldx, x_off, x_bias, taps, conv_bias, tail, tok_first, tok_slot, tok_pos, C, K);
   else
     RB_FAIL("rb_conv_causal: unknown dtype %d", x_dtype);
   RB_CHECK_LAUNCH("rb_conv_causal");
@@ -424,11 +496,11 @@ RB_EXPORT int rb_conv_causal(float* u, const void* x, int64_t ldx, int x_off, in
 RB_EXPORT int rb_gated_scan(void* out, int out_dtype, const float* u, const float* gates, const float* gate_r_bias,
                             const float* gate_i_bias, const float* lam, float decay_scale, const void* xy, int64_t ldxy,
                             int xy_dtype, int x_off, int y_off, const float* x_bias, const float* y_bias, float* state,
-                            float* tail, const int* seq_first, const int* seq_count, const int* tok_slot, int n_seq, int n_rows,
-                            int W, int Wb, int K, cudaStream_t stream) {
+                            float* tail, const int* seq_first, const int* seq_count, const int* tok_slot, const int* tok_pos, int n_seq,
+                            int n_rows, int W, int Wb, int K, cudaStream_t stream) {
   if (n_seq == 0) return 0;
   RB_REQUIRE(W > 0 && Wb > 0 && W % Wb == 0, "rb_gated_scan: width %d is not made of blocks of %d", W, Wb);
-  RB_REQUIRE(K >= 1 && K <= 9, "rb_gated_scan: %d taps (1..9 are built)", K);
+  RB_REQUIRE(K >= 1, "rb_gated_scan: %d taps", K);
   if (seq_first != nullptr && seq_count != nullptr) {
     // runs of several rows (a prompt, or a portion of one): decays and drives for all rows at once, then the chunked scan
     RB_REQUIRE(n_rows > 0, "rb_gated_scan: runs of several rows need the number of rows");
@@ -441,7 +513,7 @@ RB_EXPORT int rb_gated_scan(void* out, int out_dtype, const float* u, const floa
 #define CLAUNCH(TI, TO)                                                                                              \
   RB_LAUNCH("gated_scan_chunked_kernel", (gated_scan_chunked_kernel<TI, TO>), cgrid, SCAN_CH * SCAN_CHUNKS, 0, stream, \
             (TO*)out, gates, (const TI*)xy, ldxy, x_off, y_off, x_bias, y_bias, state, tail, seq_first, seq_count,   \
-            tok_slot, W, Wb, K)
+            tok_slot, tok_pos, W, Wb, K)
     if (xy_dtype == RB_F32 && out_dtype == RB_F32) CLAUNCH(float, float);
     else if (xy_dtype == RB_F32 && out_dtype == RB_BF16) CLAUNCH(float, __nv_bfloat16);
     else if (xy_dtype == RB_BF16 && out_dtype == RB_BF16) CLAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -454,13 +526,45 @@ RB_EXPORT int rb_gated_scan(void* out, int out_dtype, const float* u, const floa
 #define LAUNCH(TI, TO)                                                                                              \
   RB_LAUNCH("gated_scan_kernel", (gated_scan_kernel<TI, TO>), grid, 64, 0, stream, (TO*)out, u, gates, gate_r_bias,  \
             gate_i_bias, lam, decay_scale, (const TI*)xy, ldxy, x_off, y_off, x_bias, y_bias, state, tail, seq_first, \
-            seq_count, tok_slot, W, Wb, K)
+            seq_count, tok_slot, tok_pos, W, Wb, K)
   if (xy_dtype == RB_F32 && out_dtype == RB_F32) LAUNCH(float, float);
   else if (xy_dtype == RB_F32 && out_dtype == RB_BF16) LAUNCH(float, __nv_bfloat16);
   else if (xy_dtype == RB_BF16 && out_dtype == RB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else RB_FAIL("rb_gated_scan: unsupported dtypes %d -> %d", xy_dtype, out_dtype);
 #undef LAUNCH
   RB_CHECK_LAUNCH("rb_gated_scan");
+  return 0;
+}
+
+// Rows of which each is its own sequence, at most rb_gated_step_max_rows(): everything from the projections' rows to
+// S_t * gelu_tanh(y_t) in one launch.  w_gates: [blocks, 2 Wb, Wb] float32 (recurrence gate's rows, then the input gate's).
+RB_EXPORT int rb_gated_step_max_rows() { return STEP_MAX_ROWS; }
+
+RB_EXPORT int rb_gated_step(void* out, int out_dtype, const void* xy, int64_t ldxy, int xy_dtype, int x_off, int y_off,
+                            const float* x_bias, const float* y_bias, const float* taps, const float* conv_bias,
+                            const float* w_gates, const float* gate_r_bias, const float* gate_i_bias, const float* lam,
+                            float decay_scale, float* state, float* tail, const int* tok_slot, const int* tok_pos, int T, int W,
+                            int Wb, int K, cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(T <= STEP_MAX_ROWS, "rb_gated_step: %d rows (at most %d)", T, STEP_MAX_ROWS);
+  RB_REQUIRE(W > 0 && Wb > 0 && W % Wb == 0 && K >= 1, "rb_gated_step: bad sizes W=%d Wb=%d K=%d", W, Wb, K);
+  const size_t smem = ((size_t)T * Wb + (size_t)T * 2 * STEP_CH) * sizeof(float);
+  RB_REQUIRE(smem <= 200 * 1024, "rb_gated_step: blocks of %d channels do not fit shared memory", Wb);
+  const dim3 grid(W / Wb, (Wb + STEP_CH - 1) / STEP_CH);
+#define LAUNCH(TI, TO)                                                                                                \
+  do {                                                                                                                \
+    if (smem > 48 * 1024)                                                                                             \
+      RB_CUDA(cudaFuncSetAttribute(gated_step_kernel<TI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    RB_LAUNCH("gated_step_kernel", (gated_step_kernel<TI, TO>), grid, 256, smem, stream, (TO*)out, (const TI*)xy, ldxy, \
+              x_off, y_off, x_bias, y_bias, taps, conv_bias, w_gates, gate_r_bias, gate_i_bias, lam, decay_scale, state, \
+              tail, tok_slot, tok_pos, T, W, Wb, K);                                                                  \
+  } while (0)
+  if (xy_dtype == RB_F32 && out_dtype == RB_F32) LAUNCH(float, float);
+  else if (xy_dtype == RB_F32 && out_dtype == RB_BF16) LAUNCH(float, __nv_bfloat16);
+  else if (xy_dtype == RB_BF16 && out_dtype == RB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else RB_FAIL("rb_gated_step: unsupported dtypes %d -> %d", xy_dtype, out_dtype);
+#undef LAUNCH
+  RB_CHECK_LAUNCH("rb_gated_step");
   return 0;
 }
 

@@ -30,8 +30,10 @@ _SIGNATURES = {
     "rb_norm_rotate_append": [P, P, L, I, P, P, F, P, F, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P],
     "rb_head_gate": [P, P, P, L, I, I, I, I, I, P],
     "rb_gated_act": [P, P, I, I, I, I, L, I, F, F, F, P],
-    "rb_conv_causal": [P, P, L, I, I, P, P, P, P, P, P, I, I, I, P],
-    "rb_gated_scan": [P, I, P, P, P, P, P, F, P, L, I, I, I, P, P, P, P, P, P, P, I, I, I, I, I, P],
+    "rb_conv_causal": [P, P, L, I, I, P, P, P, P, P, P, P, I, I, I, P],
+    "rb_gated_step": [P, I, P, L, I, I, I, P, P, P, P, P, P, P, P, F, P, P, P, P, I, I, I, I, P],
+    "rb_gated_step_max_rows": [],
+    "rb_gated_scan": [P, I, P, P, P, P, P, F, P, L, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
     "rb_matrix_memory": [P, P, L, I, I, I, I, I, I, P, P, F, F, F, P, P, P, P, P, P, I, I, I, I, P],
     "rb_matrix_memory_lanes": [I],
     "rb_head_norm_gate": [P, I, P, P, P, L, I, I, I, I, I, F, P],

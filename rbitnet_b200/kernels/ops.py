@@ -122,6 +122,8 @@ class CudaOps:
         self.fuse_streams = True
         #: a limited gated activation is applied in the tensor-core product's epilogue (else by a kernel of its own)
         self.fuse_gated_act = True
+        #: a decode step's gated linear recurrence (convolution, gates, scan) is one kernel for up to 16 rows
+        self.fuse_recurrent_step = True
         #: tensor-core products of more than 256 tokens may share a weight tile's inner dimension
         #: between teams of CTAs (needs the workspace; tiles are taken in turn without it)
         _give_gemm_workspace(self.lib, self.device)
@@ -585,17 +587,25 @@ class CudaOps:
         first, count, tok_first, n_seq = self._runs(meta)
         f = p.f32
         tail = state.get("tail")
+        out = torch.empty((T, W), dtype=self.dtype, device=self.device)
+        if first is None and T <= self.lib.raw("rb_gated_step_max_rows")() and self.fuse_recurrent_step:
+            # a decode step: convolution, gates, recurrence and output in one launch
+            self.lib.call("rb_gated_step", _ptr(out), self.code, _ptr(proj), proj.stride(0), F32, 0, W, _ptr(f["x.b"]),
+                          _ptr(f["y.b"]), _ptr(f["conv"]), _ptr(f["conv.b"]), _ptr(p.w_gates), _ptr(f["ra.b"]), _ptr(f["ri.b"]),
+                          _ptr(f["lam"]), float(p.decay_scale), _ptr(state["S"]), _ptr(tail), _ptr(meta.tok_slot),
+                          _ptr(meta.tok_pos), T, W, Wb, K, self._stream())
+            return out
         u = torch.empty((T, W), dtype=torch.float32, device=self.device)
         self.lib.call("rb_conv_causal", _ptr(u), _ptr(proj), proj.stride(0), 0, F32, _ptr(f["x.b"]), _ptr(f["conv"]),
-                      _ptr(f["conv.b"]), _ptr(tail), _ptr(tok_first), _ptr(meta.tok_slot), T, W, K, self._stream())
+                      _ptr(f["conv.b"]), _ptr(tail), _ptr(tok_first), _ptr(meta.tok_slot), _ptr(meta.tok_pos), T, W, K,
+                      self._stream())
         gates = torch.empty((T, B, 2 * Wb), dtype=torch.float32, device=self.device)
         self.lib.call("rb_gemm_simple_batched", _ptr(gates), gates.stride(0), F32, _ptr(u), u.stride(0), _ptr(p.w_gates), Wb,
                       F32, T, 2 * Wb, Wb, 0, 1.0, B, 2 * Wb, Wb, 2 * Wb * Wb, self._stream())
-        out = torch.empty((T, W), dtype=self.dtype, device=self.device)
         self.lib.call("rb_gated_scan", _ptr(out), self.code, _ptr(u), _ptr(gates), _ptr(f["ra.b"]), _ptr(f["ri.b"]),
                       _ptr(f["lam"]), float(p.decay_scale), _ptr(proj), proj.stride(0), F32, 0, W, _ptr(f["x.b"]),
-                      _ptr(f["y.b"]), _ptr(state["S"]), _ptr(tail), _ptr(first), _ptr(count), _ptr(meta.tok_slot), n_seq,
-                      T, W, Wb, K, self._stream(), launches=1 if first is None else 2)
+                      _ptr(f["y.b"]), _ptr(state["S"]), _ptr(tail), _ptr(first), _ptr(count), _ptr(meta.tok_slot),
+                      _ptr(meta.tok_pos), n_seq, T, W, Wb, K, self._stream(), launches=1 if first is None else 2)
         return out
 
     def matrix_memory(self, proj: torch.Tensor, p, state, meta) -> torch.Tensor:

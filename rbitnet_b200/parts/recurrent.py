@@ -8,7 +8,8 @@ unit): two branches of ``inner`` channels from the same input rows h,
     a = exp(-c r softplus(lam)),  S_t = a S_(t-1) + sqrt(1 - a^2) i u,  S_(-1) = 0
     result = Wo (S_t * y)
 
-with c = 8.  State per sequence: S [inner] and the convolution's last K-1 inputs [K-1, inner].
+with c = 8.  State per sequence: S [inner] and the convolution's last inputs, kept as a ring of K rows by
+position [K, inner] (the input of position q at row q mod K).
 
 ``MatrixMemory`` (the matrix memory cell of xLSTM): per head, keys and queries of ``head_dim``
 and values of ``value_dim``,
@@ -56,7 +57,7 @@ class GatedLinearRecurrence(Mixer):
     def state_need(self):
         need = {"S": StateNeed((self.inner,))}
         if self.taps > 1:
-            need["tail"] = StateNeed((self.taps - 1, self.inner))
+            need["tail"] = StateNeed((self.taps, self.inner))
         return need
 
     def bind(self, weights, ops):

@@ -244,14 +244,18 @@ def test_gated_recurrence_kernels(ops32, W, B, K):
         ops = ops32
         def state_view(self, entry):
             return state
-    for cuts in ([0, T], [0, 1, 2, 3, 4, 30, T - 1, T], list(range(T + 1))):
+    # single rows take one fused kernel (convolution, gates, recurrence); with it switched off, the kernels of a prompt
+    for cuts, fused in (([0, T], True), ([0, 1, 2, 3, 4, 30, T - 1, T], True), (list(range(T + 1)), True),
+                        (list(range(T + 1)), False), ([0, 2, 3, 40, 41, T], False)):
+        ops32.fuse_recurrent_step = fused
         state = {k: torch.zeros((2, *n.shape), device="cuda") for k, n in part.state_need().items()}
         outs = []
         for a, b in zip(cuts[:-1], cuts[1:]):
             ctx = Ctx()
             ctx.meta = _meta(ops32, [(1, a, b - a)])
             outs.append(part.forward(ctx, h[a:b].float().cuda(), 0))
-        assert rel_err(torch.cat(outs).cpu(), want) <= 2e-4, cuts
+        ops32.fuse_recurrent_step = True
+        assert rel_err(torch.cat(outs).cpu(), want) <= 2e-4, (cuts, fused)
 
 
 @pytest.mark.parametrize("T,fused", [(19, True), (19, False), (300, True), (700, True)])

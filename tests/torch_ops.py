@@ -162,7 +162,7 @@ class TorchOps:
             xx = proj[first:first + n, :W].float() + f["x.b"]
             y = proj[first:first + n, W:].float() + f["y.b"]
             y = 0.5 * y * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (y + 0.044715 * y ** 3)))
-            old = state["tail"][slot] if K > 1 else torch.zeros(0, W)
+            old = state["tail"][slot][1:] if K > 1 else torch.zeros(0, W)     # this stand-in keeps the last K-1 inputs in rows 1..
             hist = torch.cat([old, xx], dim=0)                    # K-1 earlier inputs, then this run's
             S = state["S"][slot].clone()
             for t in range(n):
@@ -176,7 +176,7 @@ class TorchOps:
                 out[first + t] = S * y[t]
             state["S"][slot] = S
             if K > 1:
-                state["tail"][slot] = hist[n:n + K - 1]
+                state["tail"][slot][1:] = hist[n:n + K - 1]
         return out.to(self.dtype)
 
     def matrix_memory(self, proj, p, state, meta):
