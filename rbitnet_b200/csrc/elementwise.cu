@@ -536,7 +536,7 @@ __global__ void __launch_bounds__(256) norm_rotate_append_kernel(
     T* __restrict__ q_out, const T* __restrict__ proj, int64_t ld, const float* __restrict__ q_norm_w,
     const float* __restrict__ k_norm_w, float eps, const double* __restrict__ freq, float magnitude,
     const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, RbPagedLayer cache, int H, int D, int Dv,
-    int rot_dim, int interleaved, int write_kv) {
+    int rot_dim, int interleaved, int write_kv, int heads_per_block) {
   rb_pdl_launch_dependents();
   __shared__ float scratch[33];
   extern __shared__ float s_sincos[];              // rot_dim/2 sines, then as many cosines, of this token's position
@@ -566,8 +566,12 @@ __global__ void __launch_bounds__(256) norm_rotate_append_kernel(
   __syncthreads();                                 // the table is complete (also without a norm's sums before)
   T* kdst = (T*)cache.k;
   T* vdst = (T*)cache.v;
+  // With few tokens a token's heads (q heads, k heads, then v heads) are spread over several blocks, each of which
+  // makes the norms' sums for itself.
+  const int h0 = blockIdx.y * heads_per_block, h1 = h0 + heads_per_block;
+  const int r0 = min(h0, n_rot_heads), r1 = min(h1, n_rot_heads);
   // one output value per thread and turn: a q or k head's value (normed, turned or passed), or padding
-  for (int idx = threadIdx.x; idx < n_rot_heads * Dc; idx += blockDim.x) {
+  for (int idx = threadIdx.x + r0 * Dc; idx < r1 * Dc; idx += blockDim.x) {
     const int head = idx / Dc, e = idx % Dc;
     const bool is_q = head < H;
     T* dst = is_q ? q_out + ((int64_t)t * H + head) * Dc : kdst + rb_page_offset(cache, slot, pos, head - H);
@@ -592,7 +596,8 @@ __global__ void __launch_bounds__(256) norm_rotate_append_kernel(
   }
   if (write_kv) {
     const T* vsrc = row + (int64_t)(H + Kh) * D;
-    for (int idx = threadIdx.x; idx < Kh * Dc; idx += blockDim.x) {
+    const int v0 = min(max(h0 - n_rot_heads, 0), Kh), v1 = min(max(h1 - n_rot_heads, 0), Kh);
+    for (int idx = threadIdx.x + v0 * Dc; idx < v1 * Dc; idx += blockDim.x) {
       const int kvh = idx / Dc, e = idx % Dc;
       vdst[rb_page_offset(cache, slot, pos, kvh) + e] = e < Dv ? vsrc[kvh * Dv + e] : rb_from_float<T>(0.f);
     }
@@ -611,10 +616,16 @@ RB_EXPORT int rb_norm_rotate_append(void* q_out, const void* proj, int64_t ld, i
   RB_REQUIRE(rot_dim >= 0 && rot_dim <= D && rot_dim % 2 == 0 && (rot_dim == 0 || freq != nullptr),
              "rb_norm_rotate_append: the rotated prefix %d must be even and at most the head size %d", rot_dim, D);
   RbPagedLayer c{cache_k, cache_v, page_table, max_pages, page_size, Kh, Dc};
+  // few tokens: spread a token's heads over several blocks so that enough blocks run
+  const int n_heads = H + (write_kv ? 2 * Kh : 0);
+  int by = T >= 128 ? 1 : (128 + T - 1) / T;
+  if (by > n_heads) by = n_heads;
+  const int hpb = (n_heads + by - 1) / by;
+  const dim3 grid(T, (n_heads + hpb - 1) / hpb);
   if (dtype == RB_F32)
-    RB_LAUNCH("norm_rotate_append_kernel", (norm_rotate_append_kernel<float>), T, 256, (size_t)rot_dim * sizeof(float), stream, (float*)q_out, (const float*)proj, ld, q_norm_w, k_norm_w, eps, freq, magnitude, tok_pos, tok_slot, c, H, D, Dv, rot_dim, interleaved, write_kv);
+    RB_LAUNCH("norm_rotate_append_kernel", (norm_rotate_append_kernel<float>), grid, 256, (size_t)rot_dim * sizeof(float), stream, (float*)q_out, (const float*)proj, ld, q_norm_w, k_norm_w, eps, freq, magnitude, tok_pos, tok_slot, c, H, D, Dv, rot_dim, interleaved, write_kv, hpb);
   else if (dtype == RB_BF16)
-    RB_LAUNCH("norm_rotate_append_kernel", (norm_rotate_append_kernel<__nv_bfloat16>), T, 256, (size_t)rot_dim * sizeof(float), stream, (__nv_bfloat16*)q_out, (const __nv_bfloat16*)proj, ld, q_norm_w, k_norm_w, eps, freq, magnitude, tok_pos, tok_slot, c, H, D, Dv, rot_dim, interleaved, write_kv);
+    RB_LAUNCH("norm_rotate_append_kernel", (norm_rotate_append_kernel<__nv_bfloat16>), grid, 256, (size_t)rot_dim * sizeof(float), stream, (__nv_bfloat16*)q_out, (const __nv_bfloat16*)proj, ld, q_norm_w, k_norm_w, eps, freq, magnitude, tok_pos, tok_slot, c, H, D, Dv, rot_dim, interleaved, write_kv, hpb);
   else
     RB_FAIL("rb_norm_rotate_append: unknown dtype %d", dtype);
   RB_CHECK_LAUNCH("rb_norm_rotate_append");

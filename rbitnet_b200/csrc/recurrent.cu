@@ -171,73 +171,97 @@ __global__ void __launch_bounds__(SCAN_CH * SCAN_CHUNKS) gated_scan_chunked_kern
 }
 
 // ---- a few rows, each its own sequence (a decode step): convolution, gates, recurrence and output in one kernel
-// One block per (block of the gates' matrices, 32 of its channels).  It convolves all Wb channels of the block for every
-// row (the gates of a channel read them all), its warps take the 64 rows of the two gate matrices that belong to its
-// channels (a row's weights are read once, by lanes, and serve every token), and one thread per (row, channel) finishes.
-constexpr int STEP_CH = 32, STEP_MAX_ROWS = 16;
+// One block per (block of the gates' matrices, STEP_CH of its channels), one warp per channel.  The block convolves all
+// Wb channels of the gates' block for every row (the gates of a channel read them all); a warp reads its channel's two
+// rows of weights once, by lanes and eight loads at a time, for all rows' sums; lane t then finishes row t.
+constexpr int STEP_CH = 8, STEP_MAX_ROWS = 16;
 template <typename TI, typename TO>
-__global__ void __launch_bounds__(256) gated_step_kernel(
+__global__ void __launch_bounds__(32 * STEP_CH) gated_step_kernel(
     TO* __restrict__ out, const TI* __restrict__ xy, int64_t ldxy, int x_off, int y_off, const float* __restrict__ x_bias,
     const float* __restrict__ y_bias, const float* __restrict__ taps, const float* __restrict__ conv_bias,
     const float* __restrict__ w_gates, const float* __restrict__ gate_r_bias, const float* __restrict__ gate_i_bias,
     const float* __restrict__ lam, float decay_scale, float* __restrict__ state, float* __restrict__ tail,
     const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, int T, int W, int Wb, int K) {
   rb_pdl_launch_dependents();
-  extern __shared__ float s_u[];                 // [T][Wb], then the gates' sums [T][2][STEP_CH]
-  float* s_g = s_u + T * Wb;
-  const int b = blockIdx.x, ch0 = blockIdx.y * STEP_CH;
+  extern __shared__ float s_u[];                 // [T][Wb]
+  const int b = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int o = blockIdx.y * STEP_CH + warp;      // this warp's channel within the block
+  const bool has = o < Wb;
+  const int c = b * Wb + (has ? o : 0);
+  // the channel's two rows of weights do not depend on the kernel before: the first eight loads start now
+  const float* wr = w_gates + ((int64_t)b * 2 * Wb + (has ? o : 0)) * Wb;
+  const float* wi = wr + (int64_t)Wb * Wb;
+  float w0[4], w1[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = lane + 32 * j;
+    w0[j] = i < Wb ? wr[i] : 0.f;
+    w1[j] = i < Wb ? wi[i] : 0.f;
+  }
+  const float sp = decay_scale * softplusf_(lam[c]);
+  const float br = gate_r_bias[c], bi = gate_i_bias[c];
   rb_pdl_wait();
   for (int idx = threadIdx.x; idx < T * Wb; idx += blockDim.x) {
-    const int t = idx / Wb, i = idx - t * Wb, c = b * Wb + i;
+    const int t = idx / Wb, i = idx - t * Wb, cc = b * Wb + i;
     const int slot = tok_slot[t], pos = tok_pos[t];
-    float acc = conv_bias != nullptr ? conv_bias[c] : 0.f;
+    float acc = conv_bias != nullptr ? conv_bias[cc] : 0.f;
     for (int d = 0; d < K; ++d) {
       float v;
-      if (d == 0) v = rb_to_float<TI>(xy[(int64_t)t * ldxy + x_off + c]) + (x_bias != nullptr ? x_bias[c] : 0.f);
+      if (d == 0) v = rb_to_float<TI>(xy[(int64_t)t * ldxy + x_off + cc]) + (x_bias != nullptr ? x_bias[cc] : 0.f);
       else if (pos - d < 0) v = 0.f;
-      else v = tail[((int64_t)slot * K + (pos - d) % K) * W + c];
-      acc = fmaf(taps[(int64_t)c * K + (K - 1 - d)], v, acc);
+      else v = tail[((int64_t)slot * K + (pos - d) % K) * W + cc];
+      acc = fmaf(taps[(int64_t)cc * K + (K - 1 - d)], v, acc);
     }
     s_u[idx] = acc;
   }
   __syncthreads();
-  const int n_ch = min(STEP_CH, Wb - ch0);
-  for (int rr = warp; rr < 2 * n_ch; rr += (blockDim.x >> 5)) {
-    const int which = rr / n_ch, o = ch0 + rr % n_ch;
-    const float* wrow = w_gates + ((int64_t)b * 2 * Wb + (int64_t)which * Wb + o) * Wb;
-    float acc[STEP_MAX_ROWS];
+  float ar[STEP_MAX_ROWS], ai[STEP_MAX_ROWS];
 #pragma unroll
-    for (int t = 0; t < STEP_MAX_ROWS; ++t) acc[t] = 0.f;
-    for (int i = lane; i < Wb; i += 32) {
-      const float w = wrow[i];
+  for (int t = 0; t < STEP_MAX_ROWS; ++t) ar[t] = ai[t] = 0.f;
+  for (int i0 = 0; i0 < Wb; i0 += 128) {
+    if (i0 > 0) {
 #pragma unroll
-      for (int t = 0; t < STEP_MAX_ROWS; ++t)
-        if (t < T) acc[t] = fmaf(w, s_u[t * Wb + i], acc[t]);
+      for (int j = 0; j < 4; ++j) {
+        const int i = i0 + lane + 32 * j;
+        w0[j] = i < Wb ? wr[i] : 0.f;
+        w1[j] = i < Wb ? wi[i] : 0.f;
+      }
     }
 #pragma unroll
-    for (int t = 0; t < STEP_MAX_ROWS; ++t) {
-      if (t < T) {
-        const float v = rb_warp_sum(acc[t]);
-        if (lane == 0) s_g[(t * 2 + which) * STEP_CH + rr % n_ch] = v;
+    for (int j = 0; j < 4; ++j) {
+      const int i = i0 + lane + 32 * j;
+      if (i < Wb) {
+#pragma unroll
+        for (int t = 0; t < STEP_MAX_ROWS; ++t)
+          if (t < T) {
+            const float u = s_u[t * Wb + i];
+            ar[t] = fmaf(w0[j], u, ar[t]);
+            ai[t] = fmaf(w1[j], u, ai[t]);
+          }
       }
     }
   }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < T * n_ch; idx += blockDim.x) {
-    const int t = idx / n_ch, ch = idx - t * n_ch, c = b * Wb + ch0 + ch;
-    const int slot = tok_slot[t], pos = tok_pos[t];
-    const float r = sigmoidf_(s_g[(t * 2) * STEP_CH + ch] + gate_r_bias[c]);
-    const float in = sigmoidf_(s_g[(t * 2 + 1) * STEP_CH + ch] + gate_i_bias[c]);
-    const float a = expf(-decay_scale * softplusf_(lam[c]) * r);
-    float S = state[(int64_t)slot * W + c];
-    S = fmaf(a, S, sqrtf(1.0f - a * a) * in * s_u[t * Wb + ch0 + ch]);
-    state[(int64_t)slot * W + c] = S;
-    const float y = gelu_tanh_(rb_to_float<TI>(xy[(int64_t)t * ldxy + y_off + c]) + (y_bias != nullptr ? y_bias[c] : 0.f));
-    out[(int64_t)t * W + c] = rb_from_float<TO>(S * y);
-    if (K > 1)
-      tail[((int64_t)slot * K + pos % K) * W + c] = rb_to_float<TI>(xy[(int64_t)t * ldxy + x_off + c]) + (x_bias != nullptr ? x_bias[c] : 0.f);
+  float gr = 0.f, gi = 0.f;                       // lane t keeps row t's sums
+#pragma unroll
+  for (int t = 0; t < STEP_MAX_ROWS; ++t) {
+    if (t < T) {
+      const float a = rb_warp_sum(ar[t]), bsum = rb_warp_sum(ai[t]);
+      if (lane == t) { gr = a; gi = bsum; }
+    }
   }
+  if (!has || lane >= T) return;
+  const int t = lane;
+  const int slot = tok_slot[t], pos = tok_pos[t];
+  const float r = sigmoidf_(gr + br), in = sigmoidf_(gi + bi);
+  const float a = expf(-sp * r);
+  float S = state[(int64_t)slot * W + c];
+  S = fmaf(a, S, sqrtf(1.0f - a * a) * in * s_u[t * Wb + o]);
+  state[(int64_t)slot * W + c] = S;
+  const float y = gelu_tanh_(rb_to_float<TI>(xy[(int64_t)t * ldxy + y_off + c]) + (y_bias != nullptr ? y_bias[c] : 0.f));
+  out[(int64_t)t * W + c] = rb_from_float<TO>(S * y);
+  if (K > 1)
+    tail[((int64_t)slot * K + pos % K) * W + c] = rb_to_float<TI>(xy[(int64_t)t * ldxy + x_off + c]) + (x_bias != nullptr ? x_bias[c] : 0.f);
 }
 
 // ---------------------------------------------------------------- matrix memory
@@ -548,14 +572,14 @@ RB_EXPORT int rb_gated_step(void* out, int out_dtype, const void* xy, int64_t ld
   if (T == 0) return 0;
   RB_REQUIRE(T <= STEP_MAX_ROWS, "rb_gated_step: %d rows (at most %d)", T, STEP_MAX_ROWS);
   RB_REQUIRE(W > 0 && Wb > 0 && W % Wb == 0 && K >= 1, "rb_gated_step: bad sizes W=%d Wb=%d K=%d", W, Wb, K);
-  const size_t smem = ((size_t)T * Wb + (size_t)T * 2 * STEP_CH) * sizeof(float);
+  const size_t smem = (size_t)T * Wb * sizeof(float);
   RB_REQUIRE(smem <= 200 * 1024, "rb_gated_step: blocks of %d channels do not fit shared memory", Wb);
   const dim3 grid(W / Wb, (Wb + STEP_CH - 1) / STEP_CH);
 #define LAUNCH(TI, TO)                                                                                                \
   do {                                                                                                                \
     if (smem > 48 * 1024)                                                                                             \
       RB_CUDA(cudaFuncSetAttribute(gated_step_kernel<TI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    RB_LAUNCH("gated_step_kernel", (gated_step_kernel<TI, TO>), grid, 256, smem, stream, (TO*)out, (const TI*)xy, ldxy, \
+    RB_LAUNCH("gated_step_kernel", (gated_step_kernel<TI, TO>), grid, 32 * STEP_CH, smem, stream, (TO*)out, (const TI*)xy, ldxy, \
               x_off, y_off, x_bias, y_bias, taps, conv_bias, w_gates, gate_r_bias, gate_i_bias, lam, decay_scale, state, \
               tail, tok_slot, tok_pos, T, W, Wb, K);                                                                  \
   } while (0)
