@@ -61,7 +61,17 @@ CFG_C = {"architecture": "Safuvik", "vocab": 48, "width": 48, "norm": {"eps": 1e
          "layers": [parallel_layer(_left(3, 1, 24, 24, None, None, scale=0.5), 24, 2, 4, dense(64, 1.5)),
                     parallel_layer(_left(2, 1, 16, 8, 64, 4, None, base=100.0, scale=0.9), 40, 5, 1, dense(64, 1.5))]}
 
-CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C}
+#: only matrix memories (no cache of keys at all); a width that the tensor-core products refuse; five streams
+CFG_D = {"architecture": "Safuvik", "vocab": 70, "width": 100, "norm": {"eps": 1e-6}, "streams": 5, "logit_scale": 1.5,
+         "layers": [memory_layer(2, 12, 20, 6.0, dense(50, 2.5)), memory_layer(5, 4, 36, 20.0, None)]}
+
+#: only parallel layers; windows of one and two tokens; one head whose keys and values have the same size; one rotated pair
+CFG_E = {"architecture": "Safuvik", "vocab": 50, "width": 64, "norm": {"eps": 1e-5}, "streams": 2,
+         "layers": [parallel_layer(_left(1, 1, 64, 64, 1, 2, None, base=10.0, scale=0.3), 64, 8, 2, dense(64, 1.0)),
+                    parallel_layer(_left(6, 3, 16, 16, 2, 16, {"factor": 8.0, "original": 8, "fast": 4.0, "slow": 1.0}, scale=0.5),
+                                   16, 1, 5, dense(48, 4.0))]}
+
+CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C, "D": CFG_D, "E": CFG_E}
 
 
 def spec_of(cfg_dict):

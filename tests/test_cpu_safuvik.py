@@ -23,12 +23,12 @@ def make_engine(cfg, tensors, max_tokens=64 * 16, graphs=False, **kw):
                   max_tokens=max_tokens, max_seq=1024, **kw)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_whole(name):
     cases.whole_and_layers(make_engine, name, TOL, n=80)
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D", "E"])
 def test_prefill_against_decoding(name):
     cases.prefill_against_decoding(make_engine, name, TOL, n=40, prompt=17)
 

@@ -21,6 +21,15 @@ TOL = {"float32": 2e-4, "bfloat16": 5e-2}
 DTYPES = ["float32", "bfloat16"]
 
 
+def tol(dtype, name=""):
+    """Configuration D is matrix memories only, with gates capped at 20: a memory's output is divided by |n . q|, which
+    is a difference of a few products at the first tokens, and the bfloat16 rounding of the layer's input rows moves
+    such an output by up to 9 % of the largest logit (measured, the same request alone or in a batch; in float32 the same
+    positions are right to 6e-6).  The band for it in bfloat16 is 12 %; a lost state or a wrong slot moves the
+    logits by more than that, and the float32 run of the same case keeps the tight band."""
+    return 0.12 if (name == "D" and dtype == "bfloat16") else TOL[dtype]
+
+
 def engine_maker(dtype):
     from rbitnet_b200.engine import Engine
 
@@ -31,15 +40,15 @@ def engine_maker(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_whole(name, dtype):
-    cases.whole_and_layers(engine_maker(dtype), name, TOL[dtype])
+    cases.whole_and_layers(engine_maker(dtype), name, tol(dtype, name))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_prefill_against_decoding(name, dtype):
-    cases.prefill_against_decoding(engine_maker(dtype), name, TOL[dtype])
+    cases.prefill_against_decoding(engine_maker(dtype), name, tol(dtype, name))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -49,9 +58,9 @@ def test_portions(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_batches(name, dtype):
-    cases.batches_against_alone(engine_maker(dtype), name, TOL[dtype])
+    cases.batches_against_alone(engine_maker(dtype), name, tol(dtype, name))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -128,7 +137,7 @@ def test_one_key_stands_out_at_the_window_edge(H, Kh, D, Dv, window, dtype):
             ops.check_errors()
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_greedy_generation_through_captured_steps(name):
     cases.greedy_generation(engine_maker("float32"), name)
 
@@ -168,7 +177,7 @@ def _meta(ops, runs):
     return build_meta(chunks, np.zeros(at, dtype=np.int32), np.zeros(0, dtype=np.int32), ops.device)
 
 
-@pytest.mark.parametrize("s,E,n_y", [(4, 96, 2), (1, 64, 1), (3, 1000, 2), (8, 40, 1)])
+@pytest.mark.parametrize("s,E,n_y", [(4, 96, 2), (1, 64, 1), (3, 1000, 2), (8, 40, 1), (5, 50, 2), (6, 64, 1), (16, 33, 3), (2, 4100, 1)])
 def test_stream_step_fused_against_pieces_and_plain(ops32, s, E, n_y):
     g = torch.Generator().manual_seed(s * 100 + E)
     T = 7
