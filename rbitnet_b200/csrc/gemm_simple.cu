@@ -74,6 +74,71 @@ __global__ void __launch_bounds__(256) gemm_simple_kernel(TC* __restrict__ C, in
   }
 }
 
+
+// The same product with tiles of 128 x 128 and 8 x 8 outputs per thread, for many rows: every value read from shared
+// memory feeds eight multiply-adds instead of four.  Each output element is still one sequential float32 sum over k in
+// ascending order.
+constexpr int LM = 128, LN = 128, LK = 16;
+
+template <typename TA, typename TC>
+__global__ void __launch_bounds__(256) gemm_simple_large_kernel(TC* __restrict__ C, int64_t ldc, const TA* __restrict__ A,
+                                                               int64_t lda, const TA* __restrict__ W, int64_t ldw, int M,
+                                                               int N, int K, int accumulate, float alpha, int64_t batch_c,
+                                                               int64_t batch_a, int64_t batch_w) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  C += blockIdx.z * batch_c;
+  A += blockIdx.z * batch_a;
+  W += blockIdx.z * batch_w;
+  __shared__ __align__(16) float As[LK][LM + 4];
+  __shared__ __align__(16) float Ws[LK][LN + 4];
+  const int m0 = blockIdx.y * LM, n0 = blockIdx.x * LN;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;      // outputs: rows ty*4 + {0..3} and 64 + ty*4 + {0..3}, columns likewise with tx
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += LK) {
+#pragma unroll
+    for (int e = threadIdx.x; e < LM * LK; e += 256) {
+      const int r = e / LK, c = e % LK;
+      const int gm = m0 + r, gn = n0 + r, gk = k0 + c;
+      As[c][r] = (gm < M && gk < K) ? rb_to_float<TA>(A[(int64_t)gm * lda + gk]) : 0.f;
+      Ws[c][r] = (gn < N && gk < K) ? rb_to_float<TA>(W[(int64_t)gn * ldw + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < LK; ++kk) {
+      const float4 a0 = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&As[kk][64 + ty * 4]);
+      const float4 w0 = *reinterpret_cast<const float4*>(&Ws[kk][tx * 4]);
+      const float4 w1 = *reinterpret_cast<const float4*>(&Ws[kk][64 + tx * 4]);
+      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int gm = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + i - 4);
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int gn = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + j - 4);
+      if (gn >= N) continue;
+      TC* p = C + (int64_t)gm * ldc + gn;
+      float v = alpha == 1.0f ? acc[i][j] : acc[i][j] * alpha;
+      if (accumulate) v += rb_to_float<TC>(*p);
+      *p = rb_from_float<TC>(v);
+    }
+  }
+}
+
 }  // namespace
 
 // a_dtype: dtype of A and W; c_dtype: dtype of C.  accumulate: C += instead of C =.
@@ -86,6 +151,21 @@ RB_EXPORT int rb_gemm_simple_batched(void* C, int64_t ldc, int c_dtype, const vo
                                      cudaStream_t stream) {
   if (M == 0 || N == 0 || n_batch == 0) return 0;
   RB_REQUIRE(M > 0 && N > 0 && K > 0, "rb_gemm_simple: bad sizes M=%d N=%d K=%d", M, N, K);
+  if (M >= 256 && N >= LN) {
+    // many rows: the larger tiles
+    dim3 lgrid((N + LN - 1) / LN, (M + LM - 1) / LM, n_batch);
+    RB_REQUIRE(lgrid.y <= 65535 && n_batch >= 1 && n_batch <= 65535, "rb_gemm_simple: M=%d, %d products: too large for one launch", M, n_batch);
+#define LLAUNCH(TA, TC)                                                                                            \
+  RB_LAUNCH("gemm_simple_large_kernel", (gemm_simple_large_kernel<TA, TC>), lgrid, 256, 0, stream, (TC*)C, ldc,     \
+            (const TA*)A, lda, (const TA*)W, ldw, M, N, K, accumulate, alpha, batch_c, batch_a, batch_w)
+    if (a_dtype == RB_F32 && c_dtype == RB_F32) LLAUNCH(float, float);
+    else if (a_dtype == RB_BF16 && c_dtype == RB_F32) LLAUNCH(__nv_bfloat16, float);
+    else if (a_dtype == RB_BF16 && c_dtype == RB_BF16) LLAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else RB_FAIL("rb_gemm_simple: unsupported dtypes a=%d c=%d", a_dtype, c_dtype);
+#undef LLAUNCH
+    RB_CHECK_LAUNCH("rb_gemm_simple");
+    return 0;
+  }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, n_batch);
   RB_REQUIRE(grid.y <= 65535 && n_batch >= 1 && n_batch <= 65535, "rb_gemm_simple: M=%d, %d products: too large for one launch", M, n_batch);
 #define LAUNCH(TA, TC)                                                                                     \
