@@ -112,3 +112,24 @@ def test_replay_runs_the_design(tmp_path):
     got2 = torch.from_numpy(np.fromfile(tmp_path / "o" / "2.f32", dtype="<f4").reshape(1, -1))
     assert not (tmp_path / "o" / "1.f32").exists()
     assert cases.rel_err(got0, ref[[0, 14]]) <= TOL and cases.rel_err(got2, ref[[19]]) <= TOL
+
+
+def test_command_line_serves_the_design(tmp_path, capsys):
+    """random -> inspect -> generate, the same verbs as for the Llama decoder."""
+    from rbitnet_b200.cli import main
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(CONFIGS["C"]))
+    assert main(["random", "--config", str(cfg_path), "--out", str(tmp_path / "m"), "--seed", "4", "--dtype", "float32"]) == 0
+    assert main(["inspect", str(tmp_path / "m")]) == 0
+    out = capsys.readouterr().out
+    assert "Safuvik: 2 layers, width 48" in out and "tensors fit the model" in out
+    assert main(["generate", "--model", str(tmp_path / "m"), "--dtype", "float32", "--prompt-ids", "1 2 3", "--max-tokens", "5",
+                 "--temperature", "0", "--max-seq", "256", "--cache-tokens", "256"], ops=TorchOps(torch.float32)) == 0
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    from rbitnet_b200.weights import read_model_tensors
+    tensors = read_model_tensors(tmp_path / "m")
+    seq = [1, 2, 3]
+    for t in line["tokens"]:
+        assert int(torch.argmax(plain.forward(CONFIGS["C"], tensors, seq)[-1])) == t
+        seq.append(t)
+    assert len(line["tokens"]) == 5
