@@ -604,6 +604,95 @@ __global__ void __launch_bounds__(256) norm_rotate_append_kernel(
   }
 }
 
+// The same for bfloat16 rows whose heads are made of whole groups of eight values (D, Dv, Dc and the rotated prefix
+// multiples of 8, interleaved pairs, 16-byte aligned rows): a thread takes eight neighbouring values at a time, which
+// hold four whole pairs, with one 16-byte load and one 16-byte store.
+__global__ void __launch_bounds__(256) norm_rotate_append_rows_kernel(
+    __nv_bfloat16* __restrict__ q_out, const __nv_bfloat16* __restrict__ proj, int64_t ld, const float* __restrict__ q_norm_w,
+    const float* __restrict__ k_norm_w, float eps, const double* __restrict__ freq, float magnitude,
+    const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, RbPagedLayer cache, int H, int D, int Dv,
+    int rot_dim, int heads_per_block) {
+  rb_pdl_launch_dependents();
+  __shared__ float scratch[33];
+  extern __shared__ float s_sincos[];
+  const int t = blockIdx.x;
+  const int Dc = cache.head_dim, Kh = cache.n_kv_heads;
+  const int pos = tok_pos[t], slot = tok_slot[t];
+  for (int i = threadIdx.x; i < rot_dim / 2; i += blockDim.x)
+    rb_angle_sincos(pos, freq[i], magnitude, &s_sincos[i], &s_sincos[rot_dim / 2 + i]);
+  rb_pdl_wait();
+  const __nv_bfloat16* row = proj + (int64_t)t * ld;
+  auto sum_squares = [&](const __nv_bfloat16* src, int n) {
+    float ss = 0.f;
+    for (int e = threadIdx.x * 8; e < n; e += blockDim.x * 8) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + e);
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(p2[j]);
+        ss += f.x * f.x + f.y * f.y;
+      }
+    }
+    return rb_block_sum(ss, scratch);
+  };
+  float rq = 1.f, rk = 1.f;
+  if (q_norm_w != nullptr) rq = 1.0f / sqrtf(sum_squares(row, H * D) / (float)(H * D) + eps);
+  if (k_norm_w != nullptr) rk = 1.0f / sqrtf(sum_squares(row + H * D, Kh * D) / (float)(Kh * D) + eps);
+  __syncthreads();
+  const int n_rot_heads = H + Kh, per_head = Dc / 8;
+  const int h0 = blockIdx.y * heads_per_block, h1 = h0 + heads_per_block;
+  const int r0 = min(h0, n_rot_heads), r1 = min(h1, n_rot_heads);
+  __nv_bfloat16* kdst = (__nv_bfloat16*)cache.k;
+  __nv_bfloat16* vdst = (__nv_bfloat16*)cache.v;
+  for (int idx = threadIdx.x + r0 * per_head; idx < r1 * per_head; idx += blockDim.x) {
+    const int head = idx / per_head, e = (idx - head * per_head) * 8;
+    const bool is_q = head < H;
+    __nv_bfloat16* dst = is_q ? q_out + ((int64_t)t * H + head) * Dc : kdst + rb_page_offset(cache, slot, pos, head - H);
+    uint4 out = make_uint4(0, 0, 0, 0);
+    if (e < D) {
+      const int base = head * D + e;
+      const uint4 raw = *reinterpret_cast<const uint4*>(row + base);
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float* nw = is_q ? q_norm_w : k_norm_w;
+      const float fac = is_q ? rq : rk;
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(p2[j]);
+        v[2 * j] = f.x;
+        v[2 * j + 1] = f.y;
+      }
+      if (nw != nullptr) {
+        const float* w = nw + (is_q ? base : base - H * D);
+        const float4 wa = *reinterpret_cast<const float4*>(w), wb = *reinterpret_cast<const float4*>(w + 4);
+        const float ww[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = v[j] * fac * ww[j];
+      }
+      if (e < rot_dim) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float sn = s_sincos[e / 2 + j], cs = s_sincos[rot_dim / 2 + e / 2 + j];
+          const float a = v[2 * j], b = v[2 * j + 1];
+          v[2 * j] = a * cs - b * sn;
+          v[2 * j + 1] = b * cs + a * sn;
+        }
+      }
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    }
+    *reinterpret_cast<uint4*>(dst + e) = out;
+  }
+  const __nv_bfloat16* vsrc = row + (int64_t)(H + Kh) * D;
+  const int v0 = min(max(h0 - n_rot_heads, 0), Kh), v1 = min(max(h1 - n_rot_heads, 0), Kh);
+  for (int idx = threadIdx.x + v0 * per_head; idx < v1 * per_head; idx += blockDim.x) {
+    const int kvh = idx / per_head, e = (idx - kvh * per_head) * 8;
+    const uint4 val = e < Dv ? *reinterpret_cast<const uint4*>(vsrc + kvh * Dv + e) : make_uint4(0, 0, 0, 0);
+    *reinterpret_cast<uint4*>(vdst + rb_page_offset(cache, slot, pos, kvh) + e) = val;
+  }
+}
+
 // dtype: the type of the projections, of q_out and of the cache.  Dc: the width of q_out's and the cache's heads.
 RB_EXPORT int rb_norm_rotate_append(void* q_out, const void* proj, int64_t ld, int dtype, const float* q_norm_w,
                                     const float* k_norm_w, float eps, const double* freq, float magnitude,
@@ -622,6 +711,15 @@ RB_EXPORT int rb_norm_rotate_append(void* q_out, const void* proj, int64_t ld, i
   if (by > n_heads) by = n_heads;
   const int hpb = (n_heads + by - 1) / by;
   const dim3 grid(T, (n_heads + hpb - 1) / hpb);
+  if (dtype == RB_BF16 && write_kv && interleaved && D % 8 == 0 && Dv % 8 == 0 && Dc % 8 == 0 && rot_dim % 8 == 0 && ld % 8 == 0 &&
+      (uintptr_t)proj % 16 == 0 && (uintptr_t)q_out % 16 == 0 && (uintptr_t)cache_k % 16 == 0 && (uintptr_t)cache_v % 16 == 0 &&
+      (uintptr_t)q_norm_w % 16 == 0 && (uintptr_t)k_norm_w % 16 == 0) {
+    RB_LAUNCH("norm_rotate_append_rows_kernel", (norm_rotate_append_rows_kernel), grid, 256, (size_t)rot_dim * sizeof(float), stream,
+              (__nv_bfloat16*)q_out, (const __nv_bfloat16*)proj, ld, q_norm_w, k_norm_w, eps, freq, magnitude, tok_pos, tok_slot,
+              c, H, D, Dv, rot_dim, hpb);
+    RB_CHECK_LAUNCH("rb_norm_rotate_append");
+    return 0;
+  }
   if (dtype == RB_F32)
     RB_LAUNCH("norm_rotate_append_kernel", (norm_rotate_append_kernel<float>), grid, 256, (size_t)rot_dim * sizeof(float), stream, (float*)q_out, (const float*)proj, ld, q_norm_w, k_norm_w, eps, freq, magnitude, tok_pos, tok_slot, c, H, D, Dv, rot_dim, interleaved, write_kv, hpb);
   else if (dtype == RB_BF16)
