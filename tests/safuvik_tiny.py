@@ -71,7 +71,15 @@ CFG_E = {"architecture": "Safuvik", "vocab": 50, "width": 64, "norm": {"eps": 1e
                     parallel_layer(_left(6, 3, 16, 16, 2, 16, {"factor": 8.0, "original": 8, "fast": 4.0, "slow": 1.0}, scale=0.5),
                                    16, 1, 5, dense(48, 4.0))]}
 
-CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C, "D": CFG_D, "E": CFG_E}
+#: larger heads: key sizes of 64 and 128 (the tensor-core attention and the memory kernel's sixteen lanes per column),
+#: blocks of 128 channels, four streams
+CFG_F = {"architecture": "Safuvik", "vocab": 300, "width": 256, "norm": {"eps": 1e-6}, "streams": 4, "logit_scale": 0.25,
+         "layers": [parallel_layer(_left(4, 2, 64, 64, 100, 32, {"factor": 2.0, "original": 64, "fast": 16.0, "slow": 2.0}, scale=0.4),
+                                   256, 2, 4, dense(512, 6.0)),
+                    memory_layer(2, 128, 128, 10.0, dense(384, 2.0)),
+                    parallel_layer(_left(2, 1, 128, 96, 40, 64, None, base=5000.0, scale=0.3), 128, 4, 3, None)]}
+
+CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C, "D": CFG_D, "E": CFG_E, "F": CFG_F}
 
 
 def spec_of(cfg_dict):

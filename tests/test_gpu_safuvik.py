@@ -27,7 +27,13 @@ def tol(dtype, name=""):
     such an output by up to 9 % of the largest logit (measured, the same request alone or in a batch; in float32 the same
     positions are right to 6e-6).  The band for it in bfloat16 is 12 %; a lost state or a wrong slot moves the
     logits by more than that, and the float32 run of the same case keeps the tight band."""
-    return 0.12 if (name == "D" and dtype == "bfloat16") else TOL[dtype]
+    if name == "D" and dtype == "bfloat16":
+        return 0.12
+    # F (three layers, sharp scores over keys of 64 and 128): one position of 90 differs by 2.4 % whole and 5.2 % decoded
+    # (the other 89 by 0.4 to 1.6 %, both ways; float32 2e-5 everywhere), so its band is 8 %
+    if name == "F" and dtype == "bfloat16":
+        return 0.08
+    return TOL[dtype]
 
 
 def engine_maker(dtype):
@@ -40,25 +46,25 @@ def engine_maker(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_whole(name, dtype):
     cases.whole_and_layers(engine_maker(dtype), name, tol(dtype, name))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_prefill_against_decoding(name, dtype):
     cases.prefill_against_decoding(engine_maker(dtype), name, tol(dtype, name))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "F"])
 def test_portions(name, dtype):
-    cases.portions(engine_maker(dtype), name, TOL[dtype])
+    cases.portions(engine_maker(dtype), name, tol(dtype, name))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_batches(name, dtype):
     cases.batches_against_alone(engine_maker(dtype), name, tol(dtype, name))
 
