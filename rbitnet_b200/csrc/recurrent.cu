@@ -595,8 +595,9 @@ RB_EXPORT int rb_gated_step(void* out, int out_dtype, const void* xy, int64_t ld
 // Lanes per value column for a memory of D rows: the smallest power of two that leaves a thread at most 8 rows
 // (16 rows beyond 256, where a warp's 32 lanes are all a column has).
 RB_EXPORT int rb_matrix_memory_lanes(int D) {
+  const int rows = D <= 128 ? 8 : 16;       // larger memories: 16 rows a thread, so that a block's copies of k and q serve more columns
   int P = 1;
-  while ((D + P - 1) / P > 8 && P < 32) P *= 2;
+  while ((D + P - 1) / P > rows && P < 32) P *= 2;
   return P;
 }
 
@@ -647,7 +648,9 @@ RB_EXPORT int rb_matrix_memory(float* o_out, const void* proj, int64_t ld, int p
     case 2: GO(2, 8);
     case 4: GO(4, 8);
     case 8: GO(8, 8);
-    case 16: GO(16, 8);
+    case 16:
+      if (per <= 8) GO(16, 8);
+      GO(16, 16);
     default:
       if (per <= 8) GO(32, 8);
       GO(32, 16);

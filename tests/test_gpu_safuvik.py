@@ -212,7 +212,7 @@ def test_stream_step_fused_against_pieces_and_plain(ops32, s, E, n_y):
     assert torch.equal(ops32.streams_expand(dev(ys[0]), s), dev(ys[0]).repeat(1, s))
 
 
-@pytest.mark.parametrize("H,D,Dv", [(2, 16, 24), (1, 40, 8), (3, 100, 33), (2, 128, 64), (1, 8, 130)])
+@pytest.mark.parametrize("H,D,Dv", [(2, 16, 24), (1, 40, 8), (3, 100, 33), (2, 128, 64), (1, 8, 130), (1, 200, 40), (2, 256, 24), (1, 300, 20)])
 def test_matrix_memory_kernel(ops32, H, D, Dv):
     """Whole runs, portions and single tokens through the state, sizes that one to four lanes hold."""
     from rbitnet_b200.parts.recurrent import MatrixMemory
