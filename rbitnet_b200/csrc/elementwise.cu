@@ -233,6 +233,58 @@ RB_EXPORT int rb_rmsnorm(void* out, int out_dtype, const float* x, const float* 
 }
 
 // ---------------------------------------------------------------- rotation + cache append
+// ---------------------------------------------------------------- layer norm with weight and bias
+// out = (x - mean) / sqrt(var + eps) * w + b, var the mean of the squared deviations; float32 sums, two passes over
+// the row (the second over the deviations).  One block per row.
+template <typename TO>
+__global__ void __launch_bounds__(256) layernorm_kernel(TO* __restrict__ out, const float* __restrict__ x,
+                                                        const float* __restrict__ w, const float* __restrict__ b, int E,
+                                                        float eps) {
+  rb_pdl_launch_dependents();
+  __shared__ float scratch[33];
+  rb_pdl_wait();
+  const float* row = x + (int64_t)blockIdx.x * E;
+  float s = 0.f;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) s += row[e];
+  const float mean = rb_block_sum(s, scratch) / (float)E;
+  float v = 0.f;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) { const float d = row[e] - mean; v = fmaf(d, d, v); }
+  const float r = 1.0f / sqrtf(rb_block_sum(v, scratch) / (float)E + eps);
+  TO* dst = out + (int64_t)blockIdx.x * E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) dst[e] = rb_from_float<TO>((row[e] - mean) * r * w[e] + (b != nullptr ? b[e] : 0.f));
+}
+
+RB_EXPORT int rb_layernorm(void* out, int out_dtype, const float* x, const float* w, const float* b, int T, int E, float eps,
+                           cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(E > 0, "rb_layernorm: width %d", E);
+  const int threads = E >= 1024 ? 256 : (E >= 256 ? 128 : 64);
+  if (out_dtype == RB_F32)
+    RB_LAUNCH("layernorm_kernel", (layernorm_kernel<float>), T, threads, 0, stream, (float*)out, x, w, b, E, eps);
+  else if (out_dtype == RB_BF16)
+    RB_LAUNCH("layernorm_kernel", (layernorm_kernel<__nv_bfloat16>), T, threads, 0, stream, (__nv_bfloat16*)out, x, w, b, E, eps);
+  else
+    RB_FAIL("rb_layernorm: unknown dtype %d", out_dtype);
+  RB_CHECK_LAUNCH("rb_layernorm");
+  return 0;
+}
+
+// ---------------------------------------------------------------- x += y, float32
+__global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__ y, int64_t n) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) x[i] += y[i];
+}
+
+RB_EXPORT int rb_add_rows(float* x, const float* y, long long n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  const long long most = (long long)rb_sm_count() * 16;
+  const int blocks = (int)((n + 255) / 256 < most ? (n + 255) / 256 : most);
+  RB_LAUNCH("add_rows_kernel", (add_rows_kernel), blocks, 256, 0, stream, x, y, (int64_t)n);
+  RB_CHECK_LAUNCH("rb_add_rows");
+  return 0;
+}
+
 // For every new token: rotate each q head and each k head by the token's
 // position (angle = pos * inv_freq[i], float32; pairs (2i,2i+1) when
 // `interleaved`, else (i, i+D/2)), write q to q_out[T,H,D], the rotated k and
@@ -693,18 +745,95 @@ __global__ void __launch_bounds__(256) norm_rotate_append_rows_kernel(
   }
 }
 
+// The same rows with a norm per head AFTER the rotation: every q and k head is turned (a prefix of it) and then
+// divided by its own root mean square over its D values (no weight).  One warp per (token, head); a lane holds
+// every 32nd value of the head in registers (D up to 32 * HN_MAX).
+constexpr int HN_MAX = 16;
+template <typename T>
+__global__ void __launch_bounds__(128) rotate_headnorm_append_kernel(
+    T* __restrict__ q_out, const T* __restrict__ proj, int64_t ld, float eps, const double* __restrict__ freq, float magnitude,
+    const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, RbPagedLayer cache, int n_tokens, int H, int D, int Dv,
+    int rot_dim, int interleaved, int write_kv) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  const int Dc = cache.head_dim, Kh = cache.n_kv_heads;
+  const int per_token = H + (write_kv ? 2 * Kh : 0);
+  const int lane = threadIdx.x & 31;
+  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (int64_t)n_tokens * per_token) return;
+  const int t = (int)(item / per_token), head = (int)(item % per_token);
+  const int pos = tok_pos[t], slot = tok_slot[t];
+  const T* row = proj + (int64_t)t * ld;
+  if (head >= H + Kh) {
+    // a value head: copied, padded with zeros
+    const int kvh = head - H - Kh;
+    T* dst = (T*)cache.v + rb_page_offset(cache, slot, pos, kvh);
+    const T* src = row + (int64_t)(H + Kh) * D + kvh * Dv;
+    for (int e = lane; e < Dc; e += 32) dst[e] = e < Dv ? src[e] : rb_from_float<T>(0.f);
+    return;
+  }
+  const bool is_q = head < H;
+  T* dst = is_q ? q_out + ((int64_t)t * H + head) * Dc : (T*)cache.k + rb_page_offset(cache, slot, pos, head - H);
+  const T* src = row + (int64_t)head * D;
+  const int rhalf = rot_dim / 2;
+  float y[HN_MAX];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < HN_MAX; ++i) {
+    const int e = lane + 32 * i;
+    y[i] = 0.f;
+    if (e >= D) continue;
+    const float me = rb_to_float<T>(src[e]);
+    if (e >= rot_dim) {
+      y[i] = me;
+    } else {
+      int pair, other;
+      bool first;
+      if (interleaved) { pair = e >> 1; first = (e & 1) == 0; other = first ? e + 1 : e - 1; }
+      else { first = e < rhalf; pair = first ? e : e - rhalf; other = first ? e + rhalf : e - rhalf; }
+      float sn, cs;
+      rb_angle_sincos(pos, freq[pair], magnitude, &sn, &cs);
+      const float ot = rb_to_float<T>(src[other]);
+      y[i] = first ? me * cs - ot * sn : me * cs + ot * sn;
+    }
+    ss = fmaf(y[i], y[i], ss);
+  }
+  ss = rb_warp_sum(ss);
+  const float r = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+  for (int i = 0; i < HN_MAX; ++i) {
+    const int e = lane + 32 * i;
+    if (e < Dc) dst[e] = rb_from_float<T>(e < D ? y[i] * r : 0.f);
+  }
+}
+
 // dtype: the type of the projections, of q_out and of the cache.  Dc: the width of q_out's and the cache's heads.
+// head_norm: the norm is one per head, after the rotation, without weights (q_norm_w and k_norm_w unused).
 RB_EXPORT int rb_norm_rotate_append(void* q_out, const void* proj, int64_t ld, int dtype, const float* q_norm_w,
                                     const float* k_norm_w, float eps, const double* freq, float magnitude,
                                     const int* tok_pos, const int* tok_slot, void* cache_k, void* cache_v,
                                     const int* page_table, int max_pages, int page_size, int T, int H, int Kh, int D,
-                                    int Dv, int Dc, int rot_dim, int interleaved, int write_kv, cudaStream_t stream) {
+                                    int Dv, int Dc, int rot_dim, int interleaved, int write_kv, int head_norm,
+                                    cudaStream_t stream) {
   if (T == 0) return 0;
   RB_REQUIRE(H > 0 && Kh > 0 && D > 0 && Dv > 0 && Dc >= D && Dc >= Dv && page_size > 0,
              "rb_norm_rotate_append: bad sizes H=%d Kh=%d D=%d Dv=%d cache width %d", H, Kh, D, Dv, Dc);
   RB_REQUIRE(rot_dim >= 0 && rot_dim <= D && rot_dim % 2 == 0 && (rot_dim == 0 || freq != nullptr),
              "rb_norm_rotate_append: the rotated prefix %d must be even and at most the head size %d", rot_dim, D);
   RbPagedLayer c{cache_k, cache_v, page_table, max_pages, page_size, Kh, Dc};
+  if (head_norm) {
+    RB_REQUIRE(Dc <= 32 * HN_MAX, "rb_norm_rotate_append: a norm per head for heads of up to %d values (found %d)", 32 * HN_MAX, Dc);
+    const int64_t items = (int64_t)T * (H + (write_kv ? 2 * Kh : 0));
+    const int blocks = (int)((items + 3) / 4);
+    if (dtype == RB_F32)
+      RB_LAUNCH("rotate_headnorm_append_kernel", (rotate_headnorm_append_kernel<float>), blocks, 128, 0, stream, (float*)q_out, (const float*)proj, ld, eps, freq, magnitude, tok_pos, tok_slot, c, T, H, D, Dv, rot_dim, interleaved, write_kv);
+    else if (dtype == RB_BF16)
+      RB_LAUNCH("rotate_headnorm_append_kernel", (rotate_headnorm_append_kernel<__nv_bfloat16>), blocks, 128, 0, stream, (__nv_bfloat16*)q_out, (const __nv_bfloat16*)proj, ld, eps, freq, magnitude, tok_pos, tok_slot, c, T, H, D, Dv, rot_dim, interleaved, write_kv);
+    else
+      RB_FAIL("rb_norm_rotate_append: unknown dtype %d", dtype);
+    RB_CHECK_LAUNCH("rb_norm_rotate_append");
+    return 0;
+  }
   // few tokens: spread a token's heads over several blocks so that enough blocks run
   const int n_heads = H + (write_kv ? 2 * Kh : 0);
   int by = T >= 128 ? 1 : (128 + T - 1) / T;
@@ -732,10 +861,11 @@ RB_EXPORT int rb_norm_rotate_append(void* q_out, const void* proj, int64_t ld, i
 
 // ---------------------------------------------------------------- a gate per head on the attention's output
 // out[t, h*Dv + j] = a[t, h*Dc + j] * sigmoid(gate[t*ldg + h]) for j < Dv: drops the padding of heads that are
-// Dc wide and applies one gate value per head (no gate: gate == null).
+// Dc wide and applies one gate value per head (no gate: gate == null), or one per value (per_value:
+// gate[t*ldg + h*Dv + j]).
 template <typename T>
 __global__ void head_gate_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ gate, int64_t ldg,
-                                 int64_t n, int H, int Dv, int Dc) {
+                                 int64_t n, int H, int Dv, int Dc, int per_value) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
@@ -743,22 +873,22 @@ __global__ void head_gate_kernel(T* __restrict__ out, const T* __restrict__ a, c
     const int r = (int)(i % ((int64_t)H * Dv));
     const int h = r / Dv, j = r % Dv;
     float v = rb_to_float<T>(a[(t * H + h) * Dc + j]);
-    if (gate != nullptr) v *= 1.0f / (1.0f + expf(-rb_to_float<T>(gate[t * ldg + h])));
+    if (gate != nullptr) v *= 1.0f / (1.0f + expf(-rb_to_float<T>(gate[t * ldg + (per_value ? r : h)])));
     out[i] = rb_from_float<T>(v);
   }
 }
 
 RB_EXPORT int rb_head_gate(void* out, const void* a, const void* gate, int64_t ldg, int dtype, int T, int H, int Dv, int Dc,
-                           cudaStream_t stream) {
+                           int per_value, cudaStream_t stream) {
   if (T == 0) return 0;
   const int64_t n = (int64_t)T * H * Dv;
   const int threads = 256;
   const int64_t most = (int64_t)rb_sm_count() * 16;
   const int blocks = (int)((n + threads - 1) / threads < most ? (n + threads - 1) / threads : most);
   if (dtype == RB_F32)
-    RB_LAUNCH("head_gate_kernel", (head_gate_kernel<float>), blocks, threads, 0, stream, (float*)out, (const float*)a, (const float*)gate, ldg, n, H, Dv, Dc);
+    RB_LAUNCH("head_gate_kernel", (head_gate_kernel<float>), blocks, threads, 0, stream, (float*)out, (const float*)a, (const float*)gate, ldg, n, H, Dv, Dc, per_value);
   else if (dtype == RB_BF16)
-    RB_LAUNCH("head_gate_kernel", (head_gate_kernel<__nv_bfloat16>), blocks, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)a, (const __nv_bfloat16*)gate, ldg, n, H, Dv, Dc);
+    RB_LAUNCH("head_gate_kernel", (head_gate_kernel<__nv_bfloat16>), blocks, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)a, (const __nv_bfloat16*)gate, ldg, n, H, Dv, Dc, per_value);
   else
     RB_FAIL("rb_head_gate: unknown dtype %d", dtype);
   RB_CHECK_LAUNCH("rb_head_gate");

@@ -108,7 +108,21 @@ struct GemmParams {
   // EPI_GATED: out = g' / (1 + e^(-act_alpha g')) * (u' + act_shift), g' = min(g, act_limit), u' = clamp(u, +-act_limit)
   // (act_limit <= 0: no limit).  1, 0, 0 is SiLU(gate) * up.
   float act_alpha, act_limit, act_shift;
+  // EPI_STORE: the stored value is max(v, 0)^2 instead of v (square_relu != 0).
+  int square_relu;
+  // Grouped rows (tile_group != nullptr; one product per CTA item, K whole): the rows of X are sorted into groups
+  // whose first rows lie on token-tile borders, W holds one matrix of group_rows rows per group, one below the
+  // other, and token tile i multiplies by the matrix of group tile_group[i] (a device array the kernel before
+  // this one may have written; negative: the tile holds no rows and zeros are stored).  n_out counts one
+  // group's rows, and output columns are numbered within the group.
+  const int* tile_group;
+  int group_rows;
 };
+
+__device__ __forceinline__ float stored_value(const GemmParams& p, float v) {
+  if (p.square_relu) { v = fmaxf(v, 0.f); v *= v; }
+  return v;
+}
 
 // The gated epilogue's value, with the hardware's exponential and reciprocal: their error (a few units of
 // float32) is far below the rounding to bfloat16 that follows.
@@ -125,6 +139,7 @@ __device__ __forceinline__ float gated_value(const GemmParams& p, float g, float
 // number `part` (teams first_team .. first_team + parts - 1, in the order of their k blocks).
 struct Piece {
   int n0, t0, kb_begin, nkb;
+  int w0;          // first row of W of the tile (n0, or n0 within the tile's group)
   int w_tile, part, parts, first_team;
 };
 
@@ -225,6 +240,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = tmem_holder;
+  if (p.tile_group != nullptr) rb_pdl_wait();      // the tiles' groups are data of the kernel before this one
   // Barriers and tensor memory are ready.  Whoever touches memory that an earlier kernel may
   // still be writing or reading calls rb_pdl_wait() first: the loader before it loads X, the
   // epilogue warps before they touch C.  W is never written, so its first tiles are requested
@@ -250,7 +266,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       const long long g_begin = (long long)g * nkb_total, g_end = g_begin + nkb_total;
       const long long to = g_end < end ? g_end : end;
       s.w_tile = g;
-      s.n0 = g * BM;
+      s.n0 = s.w0 = g * BM;
       s.t0 = sk_tt * BN;
       s.kb_begin = (int)(from - g_begin);
       s.nkb = (int)(to - from);
@@ -268,6 +284,12 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     s.t0 = (tile % p.n_t_tiles) * BN;
     s.kb_begin = split * p.kb_per_split;
     s.nkb = max(0, min(nkb_total, s.kb_begin + p.kb_per_split) - s.kb_begin);
+    s.w0 = s.n0;
+    if (p.tile_group != nullptr) {
+      const int g = p.tile_group[tile % p.n_t_tiles];
+      if (g < 0) s.nkb = 0;
+      else s.w0 = g * p.group_rows + s.n0;
+    }
     s.part = 0; s.parts = 1; s.first_team = 0;
     return true;
   };
@@ -286,7 +308,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           uint8_t* stage = smem + (size_t)i * STAGE_BYTES;
           mbar_expect_tx(&full_bar[i], STAGE_BYTES);
           const int k = (s.kb_begin + i) * BK;
-          tma_load_2d(stage, &tmW, k, s.n0, &full_bar[i]);
+          tma_load_2d(stage, &tmW, k, s.w0, &full_bar[i]);
         }
         rb_pdl_wait();
         for (int i = 0; i < early; ++i) {
@@ -305,7 +327,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           uint8_t* stage = smem + (size_t)st * STAGE_BYTES;
           mbar_expect_tx(&full_bar[st], STAGE_BYTES);
           const int k = (s.kb_begin + i) * BK;
-          tma_load_2d(stage, &tmW, k, s.n0, &full_bar[st]);
+          tma_load_2d(stage, &tmW, k, s.w0, &full_bar[st]);
           tma_load_2d(stage + W_TILE_BYTES, &tmX, k, s.t0, &full_bar[st]);
         }
       }
@@ -456,7 +478,10 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) store_out<OutT>(box + j * OUT_COLS + row, __uint_as_float(r[j]) * p.alpha);
+            for (int j = 0; j < 16; ++j) {
+              const float v = __uint_as_float(r[j]) * p.alpha;
+              store_out<OutT>(box + j * OUT_COLS + row, EPI == EPI_STORE ? stored_value(p, v) : v);
+            }
           }
           fence_async_shared();
           if (issuer) bulk_wait_read_all();          // the box before this one has left its half of the staging area
@@ -518,7 +543,8 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < 16; ++j)
               if (j < t_left)
-                store_out<OutT>(dst + (int64_t)j * p.ldc, __uint_as_float(r[j]) * (normed ? p.alpha * norm_r[t0 + c + j] : p.alpha));
+                store_out<OutT>(dst + (int64_t)j * p.ldc,
+                                stored_value(p, __uint_as_float(r[j]) * (normed ? p.alpha * norm_r[t0 + c + j] : p.alpha)));
           }
         }
       }
@@ -681,7 +707,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 ((float*)p.C)[at] = now;
                 if (emit) p.emit_xb[(int64_t)(t0 + col[h]) * p.emit_ld + n] = __float2bfloat16_rn(now * g_n);
               } else {
-                store_out<OutT>((OutT*)p.C + at, v);
+                store_out<OutT>((OutT*)p.C + at, stored_value(p, v));
               }
             }
             if (emit && column) {
@@ -1053,7 +1079,24 @@ struct NormOptions {
 thread_local NormOptions t_norm;
 struct GatedAct { float alpha = 1.f, limit = 0.f, shift = 0.f; };
 thread_local GatedAct t_act;
+struct StoreOptions { int square_relu = 0; const int* tile_group = nullptr; int group_rows = 0; };
+thread_local StoreOptions t_store;
 }  // namespace
+
+// The next stored product (epilogue 0) of this thread stores max(v, 0)^2 instead of v.
+RB_EXPORT int rb_gemm_tc_square_relu() {
+  t_store.square_relu = 1;
+  return 0;
+}
+
+// The next stored product (epilogue 0) of this thread is a grouped one (see GemmParams): W holds one matrix of
+// n_out rows per group (w_rows = groups * n_out), the token tile must be given, and tile_group has one entry
+// per token tile.
+RB_EXPORT int rb_gemm_tc_grouped(const int* tile_group) {
+  RB_REQUIRE(tile_group != nullptr, "rb_gemm_tc_grouped: no tile groups");
+  t_store.tile_group = tile_group;
+  return 0;
+}
 
 // The next gated product (epilogue 3) of this thread applies g' sigmoid(alpha g') (u' + shift) with g' = min(g, limit)
 // and u' = clamp(u, -limit, limit) (limit <= 0: none) instead of SiLU(gate) * up.
@@ -1097,7 +1140,14 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
   t_norm = NormOptions();
   const GatedAct act = t_act;
   t_act = GatedAct();
+  const StoreOptions store = t_store;
+  t_store = StoreOptions();
   if (n_tokens == 0 || n_out == 0) return 0;
+  RB_REQUIRE((store.square_relu == 0 && store.tile_group == nullptr) || epilogue == EPI_STORE,
+             "rb_gemm_tc: a squared activation or grouped rows with epilogue %d (only a stored product has them)", epilogue);
+  RB_REQUIRE(store.tile_group == nullptr || (splits == 1 && token_tile > 0 && w_rows % n_out == 0),
+             "rb_gemm_tc: grouped rows want K whole, a given token tile and whole groups (splits %d, tile %d, %d rows of %d)",
+             splits, token_tile, w_rows, n_out);
   RB_REQUIRE(alpha == 1.0f || epilogue == EPI_STORE || epilogue == EPI_ADD, "rb_gemm_tc: alpha %g with epilogue %d", alpha, epilogue);
   RB_REQUIRE(n_tokens > 0 && n_out > 0 && K > 0, "rb_gemm_tc: bad sizes tokens=%d out=%d K=%d", n_tokens, n_out, K);
   RB_REQUIRE(K % 8 == 0, "rb_gemm_tc: inner size %d is not a multiple of 8", K);
@@ -1125,6 +1175,8 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
   // 28,672 rows: 1,792 tiles are twelve rounds of 148 SMs and 16 tiles, whatever power of two times
   // 224 the tiles are).  The weight tiles that whole rounds hold stay one product; the few that are
   // left become a second one on all SMs: token tiles of 64, K cut into a cluster, as for few tokens.
+  RB_REQUIRE(store.tile_group == nullptr || bn == token_tile,
+             "rb_gemm_tc: grouped rows in tiles of %d, but the output's alignment allows only %d", token_tile, bn);
   if (token_tile == 0 && bn >= 128 && splits == 1 && plan.sk_len == 0 && g_tail_for_test >= 0 &&
       (epilogue == EPI_GATED || epilogue == EPI_STORE)) {
     const long long sms = rb_sm_count(), w_tiles = (n_out + BM - 1) / BM, n_t = (n_tokens + bn - 1) / bn;
@@ -1146,6 +1198,7 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
       const int64_t out_off = epilogue == EPI_GATED ? rows_main / 2 : rows_main;       // columns of C the main product fills
       const int feat_main = epilogue == EPI_GATED ? (n_features < out_off ? n_features : (int)out_off) : 0;
       t_act = act;                 // both products of the pair apply the caller's activation
+      t_store.square_relu = store.square_relu;
       if (gemm_tc(C, ldc, c_dtype, X, ldx, n_tokens, W, ldw, rows_main, rows_main, K, epilogue, feat_main, 1, bn, nullptr,
                   alpha, stream) != 0)
         return -1;
@@ -1154,6 +1207,7 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
       const char* w_rest = (const char*)W + (int64_t)rows_main * ldw * 2;
       const int per = (nkb + parts - 1) / parts;
       t_act = act;
+      t_store.square_relu = store.square_relu;
       return gemm_tc(c_tail, ldc, c_dtype, X, ldx, n_tokens, w_rest, ldw, w_rows - rows_main, n_out - rows_main, K, epilogue,
                      epilogue == EPI_GATED ? n_features - (int)out_off : 0, (nkb + per - 1) / per, 64, nullptr, alpha, stream);
     }
@@ -1177,6 +1231,7 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
   p.cluster = splits > 1 ? 1 : 0;
   p.alpha = alpha;
   p.act_alpha = 1.f; p.act_limit = 0.f; p.act_shift = 0.f;
+  p.square_relu = store.square_relu; p.tile_group = store.tile_group; p.group_rows = n_out;
   if (epilogue == EPI_GATED) {
     p.act_alpha = act.alpha; p.act_limit = act.limit; p.act_shift = act.shift;
   }

@@ -31,7 +31,7 @@ __global__ void conv_causal_kernel(float* __restrict__ u, const TI* __restrict__
                                    const float* __restrict__ x_bias, const float* __restrict__ taps,
                                    const float* __restrict__ conv_bias, const float* __restrict__ tail,
                                    const int* __restrict__ tok_first, const int* __restrict__ tok_slot,
-                                   const int* __restrict__ tok_pos, int C, int K) {
+                                   const int* __restrict__ tok_pos, int C, int K, int silu) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
   const int t = blockIdx.x;
@@ -48,7 +48,28 @@ __global__ void conv_causal_kernel(float* __restrict__ u, const TI* __restrict__
       else v = tail[((int64_t)slot * K + (pos - d) % K) * C + c];
       acc = fmaf(taps[(int64_t)c * K + (K - 1 - d)], v, acc);
     }
-    u[(int64_t)t * C + c] = acc;
+    u[(int64_t)t * C + c] = silu ? acc * sigmoidf_(acc) : acc;
+  }
+}
+
+// The ring of a convolution's last inputs moves on to the end of every run: the inputs (with their bias) of the
+// run's last K-1 positions go to their rows.  For a mixer whose recurrence kernel does not do this itself.
+template <typename TI>
+__global__ void conv_tail_kernel(float* __restrict__ tail, const TI* __restrict__ x, int64_t ldx, int x_off,
+                                 const float* __restrict__ x_bias, const int* __restrict__ seq_first,
+                                 const int* __restrict__ seq_count, const int* __restrict__ tok_slot,
+                                 const int* __restrict__ tok_pos, int C, int K) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  const int first = seq_first != nullptr ? seq_first[blockIdx.x] : blockIdx.x;
+  const int n = seq_count != nullptr ? seq_count[blockIdx.x] : 1;
+  const int slot = tok_slot[first], pos0 = tok_pos[first];
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    const float xb = x_bias != nullptr ? x_bias[c] : 0.f;
+    for (int back = 0; back < K - 1 && back < n; ++back) {
+      const int q = pos0 + n - 1 - back;
+      tail[((int64_t)slot * K + q % K) * C + c] = rb_to_float<TI>(x[(int64_t)(first + n - 1 - back) * ldx + x_off + c]) + xb;
+    }
   }
 }
 
@@ -472,12 +493,13 @@ __global__ void __launch_bounds__(128) matrix_memory_kernel(
   if (blockIdx.z == 0 && threadIdx.x == 0) m_state[(int64_t)slot * H + h] = *s_m;
 }
 
-// Per (token, head): o / rms(o) over the head's Dv values, times the weight, times sigmoid(gate).
-// One warp each.  gate: the projections' rows, at column g_off.
+// Per (token, head): o / rms(o) over the head's Dv values, times the weight, times sigmoid(gate) (gate_silu: times
+// gate * sigmoid(gate)).  One warp each.  gate: the projections' rows, at column g_off.  The weight has H * Dv
+// values, or Dv values that every head uses (w_shared).
 template <typename TI, typename TO>
 __global__ void head_norm_gate_kernel(TO* __restrict__ out, const float* __restrict__ o, const float* __restrict__ w,
                                       const TI* __restrict__ proj, int64_t ld, int g_off, int n_rows, int H, int Dv,
-                                      float eps) {
+                                      float eps, int w_shared, int gate_silu) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -491,7 +513,8 @@ __global__ void head_norm_gate_kernel(TO* __restrict__ out, const float* __restr
   const float r = 1.0f / sqrtf(ss / (float)Dv + eps);
   for (int j = lane; j < Dv; j += 32) {
     const float g = rb_to_float<TI>(proj[(int64_t)t * ld + g_off + h * Dv + j]);
-    out[((int64_t)t * H + h) * Dv + j] = rb_from_float<TO>(row[j] * r * w[h * Dv + j] * sigmoidf_(g));
+    const float gate = gate_silu ? g * sigmoidf_(g) : sigmoidf_(g);
+    out[((int64_t)t * H + h) * Dv + j] = rb_from_float<TO>(row[j] * r * w[w_shared ? j : h * Dv + j] * gate);
   }
 }
 
@@ -499,7 +522,7 @@ __global__ void head_norm_gate_kernel(TO* __restrict__ out, const float* __restr
 
 RB_EXPORT int rb_conv_causal(float* u, const void* x, int64_t ldx, int x_off, int x_dtype, const float* x_bias,
                              const float* taps, const float* conv_bias, const float* tail, const int* tok_first,
-                             const int* tok_slot, const int* tok_pos, int T, int C, int K, cudaStream_t stream) {
+                             const int* tok_slot, const int* tok_pos, int T, int C, int K, int silu, cudaStream_t stream) {
   if (T == 0) return 0;
   RB_REQUIRE(C > 0 && K >= 1, "rb_conv_causal: bad sizes C=%d K=%d", C, K);
   const int threads = 128;
@@ -507,12 +530,32 @@ RB_EXPORT int rb_conv_causal(float* u, const void* x, int64_t ldx, int x_off, in
   if (by > 64) by = 64;
   const dim3 grid(T, by);
   if (x_dtype == RB_F32)
-    RB_LAUNCH("conv_causal_kernel", (conv_causal_kernel<float>), grid, threads, 0, stream, u, (const float*)x, ldx, x_off, x_bias, taps, conv_bias, tail, tok_first, tok_slot, tok_pos, C, K);
+    RB_LAUNCH("conv_causal_kernel", (conv_causal_kernel<float>), grid, threads, 0, stream, u, (const float*)x, ldx, x_off, x_bias, taps, conv_bias, tail, tok_first, tok_slot, tok_pos, C, K, silu);
   else if (x_dtype == RB_BF16)
-    RB_LAUNCH("conv_causal_kernel", (conv_causal_kernel<__nv_bfloat16>), grid, threads, 0, stream, u, (const __nv_bfloat16*)x, ldx, x_off, x_bias, taps, conv_bias, tail, tok_first, tok_slot, tok_pos, C, K);
+    RB_LAUNCH("conv_causal_kernel", (conv_causal_kernel<__nv_bfloat16>), grid, threads, 0, stream, u, (const __nv_bfloat16*)x, ldx, x_off, x_bias, taps, conv_bias, tail, tok_first, tok_slot, tok_pos, C, K, silu);
   else
     RB_FAIL("rb_conv_causal: unknown dtype %d", x_dtype);
   RB_CHECK_LAUNCH("rb_conv_causal");
+  return 0;
+}
+
+// n_runs runs (seq_first, seq_count; null: every one of the n_runs rows is its own run).
+RB_EXPORT int rb_conv_tail_update(float* tail, const void* x, int64_t ldx, int x_off, int x_dtype, const float* x_bias,
+                                  const int* seq_first, const int* seq_count, const int* tok_slot, const int* tok_pos,
+                                  int n_runs, int C, int K, cudaStream_t stream) {
+  if (n_runs == 0 || K <= 1) return 0;
+  RB_REQUIRE(C > 0, "rb_conv_tail_update: bad sizes C=%d", C);
+  const int threads = 128;
+  int by = (C + threads - 1) / threads;
+  if (by > 64) by = 64;
+  const dim3 grid(n_runs, by);
+  if (x_dtype == RB_F32)
+    RB_LAUNCH("conv_tail_kernel", (conv_tail_kernel<float>), grid, threads, 0, stream, tail, (const float*)x, ldx, x_off, x_bias, seq_first, seq_count, tok_slot, tok_pos, C, K);
+  else if (x_dtype == RB_BF16)
+    RB_LAUNCH("conv_tail_kernel", (conv_tail_kernel<__nv_bfloat16>), grid, threads, 0, stream, tail, (const __nv_bfloat16*)x, ldx, x_off, x_bias, seq_first, seq_count, tok_slot, tok_pos, C, K);
+  else
+    RB_FAIL("rb_conv_tail_update: unknown dtype %d", x_dtype);
+  RB_CHECK_LAUNCH("rb_conv_tail_update");
   return 0;
 }
 
@@ -659,13 +702,14 @@ RB_EXPORT int rb_matrix_memory(float* o_out, const void* proj, int64_t ld, int p
 }
 
 RB_EXPORT int rb_head_norm_gate(void* out, int out_dtype, const float* o, const float* w, const void* proj, int64_t ld,
-                                int proj_dtype, int g_off, int T, int H, int Dv, float eps, cudaStream_t stream) {
+                                int proj_dtype, int g_off, int T, int H, int Dv, float eps, int w_shared, int gate_silu,
+                                cudaStream_t stream) {
   if (T == 0) return 0;
   const int64_t items = (int64_t)T * H;
   const int blocks = (int)((items + 3) / 4);
 #define LAUNCH(TI, TO)                                                                                              \
   RB_LAUNCH("head_norm_gate_kernel", (head_norm_gate_kernel<TI, TO>), blocks, 128, 0, stream, (TO*)out, o, w,        \
-            (const TI*)proj, ld, g_off, T, H, Dv, eps)
+            (const TI*)proj, ld, g_off, T, H, Dv, eps, w_shared, gate_silu)
   if (proj_dtype == RB_F32 && out_dtype == RB_F32) LAUNCH(float, float);
   else if (proj_dtype == RB_F32 && out_dtype == RB_BF16) LAUNCH(float, __nv_bfloat16);
   else if (proj_dtype == RB_BF16 && out_dtype == RB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);

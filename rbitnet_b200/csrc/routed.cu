@@ -1,0 +1,371 @@
+// A feed-forward of routed experts: the router, the plan that sorts a step's (token, choice) pairs by expert,
+// the gather of the pairs' input rows, the grouped float32 product, and the weighted sum.
+//
+//   z = Wr h (float32), s = softmax(z) over all n outputs; the choice score of output e is s_e + c_e
+//   outputs form `groups` equal groups of neighbours; a group's score is its largest choice score, and
+//   only outputs of the `keep` best groups can be chosen; the `top` largest choice scores are chosen;
+//   a chosen output's weight is s_e (not renormalised)
+//   outputs n_experts .. n-1 are identity experts: their result is the input row itself
+//   result_t = sum over the chosen e of s_e * expert_e(h_t)
+//
+// The pairs whose expert has weights are sorted by expert into rows of a padded buffer in which every
+// expert's rows start on a tile border, so that a tile of rows multiplies by one expert's matrix
+// (tile_group[tile]: the expert, or -1 for a tile without rows).  Where a pair lands inside its
+// expert's rows depends on the order in which threads arrive; no result depends on it, because a row's
+// products are sums over k in a fixed order whatever rows are beside it, and a token's weighted sum
+// adds its choices in the order of the choice.
+#include "rb_common.cuh"
+
+namespace {
+
+// ---------------------------------------------------------------- router
+// One warp per token, with 2 n + 2 groups floats of shared memory.
+template <typename TI>
+__global__ void __launch_bounds__(128) route_kernel(int* __restrict__ ids, float* __restrict__ weights,
+                                                    const TI* __restrict__ h, int64_t ldh,
+                                                    const float* __restrict__ Wr, const float* __restrict__ correction,
+                                                    int T, int K, int n, int top, int groups, int keep) {
+  rb_pdl_launch_dependents();
+  extern __shared__ float s_route[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  float* z = s_route + (size_t)warp * (2 * n + 2 * groups);     // scores, choice scores, group scores, kept groups
+  float* choice = z + n;
+  float* gscore = choice + n;
+  rb_pdl_wait();
+  if (t >= T) return;
+  const TI* row = h + (int64_t)t * ldh;
+  for (int e = 0; e < n; ++e) {
+    const float* w = Wr + (int64_t)e * K;
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32) acc = fmaf(rb_to_float<TI>(row[k]), w[k], acc);
+    acc = rb_warp_sum(acc);
+    if (lane == 0) z[e] = acc;
+  }
+  __syncwarp();
+  float m = -INFINITY;
+  for (int e = lane; e < n; e += 32) m = fmaxf(m, z[e]);
+  m = rb_warp_max(m);
+  float sum = 0.f;
+  for (int e = lane; e < n; e += 32) sum += expf(z[e] - m);
+  sum = rb_warp_sum(sum);
+  const float inv = 1.0f / sum;
+  __syncwarp();
+  for (int e = lane; e < n; e += 32) {
+    const float s = expf(z[e] - m) * inv;
+    z[e] = s;
+    choice[e] = s + (correction != nullptr ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  // the largest value of v[0..count) that is not -inf-marked, lowest index on ties; every lane gets the index
+  auto arg_max = [&](const float* v, int count) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < count; e += 32)
+      if (v[e] > best) { best = v[e]; at = e; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    return at;
+  };
+  if (groups > 1 && keep < groups) {
+    const int per = n / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float best = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, choice[e]);
+      gscore[g] = best;
+    }
+    __syncwarp();
+    float* gkeep = gscore + groups;
+    for (int g = lane; g < groups; g += 32) gkeep[g] = 0.f;
+    __syncwarp();
+    for (int j = 0; j < keep; ++j) {
+      const int g = arg_max(gscore, groups);
+      if (g >= groups) break;                          // nothing left to take
+      __syncwarp();
+      if (lane == 0) { gscore[g] = -INFINITY; gkeep[g] = 1.f; }
+      __syncwarp();
+    }
+    for (int e = lane; e < n; e += 32)
+      if (gkeep[e / per] == 0.f) choice[e] = -INFINITY;
+    __syncwarp();
+  }
+  for (int j = 0; j < top; ++j) {
+    const int e = arg_max(choice, n);
+    __syncwarp();
+    if (lane == 0) {
+      const bool found = e < n;
+      ids[(int64_t)t * top + j] = found ? e : 0;
+      weights[(int64_t)t * top + j] = found ? z[e] : 0.f;
+      if (found) choice[e] = -INFINITY;
+    }
+    __syncwarp();
+  }
+}
+
+// ---------------------------------------------------------------- plan
+// One block.  ids: [pairs] chosen outputs.  Outputs:
+//   pos [pairs]        the pair's row in the padded buffer (-1: an identity expert)
+//   row_token [rows]   the token whose input row a buffer row holds (-1: padding)
+//   tile_group [tiles] the expert of a tile of rows (-1: none)
+__global__ void __launch_bounds__(1024) plan_kernel(int* __restrict__ pos, int* __restrict__ row_token,
+                                                    int* __restrict__ tile_group, const int* __restrict__ ids,
+                                                    int pairs, int top, int n_experts, int tile, int n_tiles) {
+  rb_pdl_launch_dependents();
+  extern __shared__ int s_plan[];       // counts [n_experts], first rows [n_experts]
+  int* counts = s_plan;
+  int* first = s_plan + n_experts;
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
+  rb_pdl_wait();
+  for (int r = threadIdx.x; r < n_tiles * tile; r += blockDim.x) row_token[r] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = ids[i];
+    pos[i] = e < n_experts ? atomicAdd(&counts[e], 1) : -1;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      first[e] = at;
+      at += (counts[e] + tile - 1) / tile * tile;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+    const int t0 = first[e] / tile, t1 = t0 + (counts[e] + tile - 1) / tile;
+    for (int i = t0; i < t1 && i < n_tiles; ++i) tile_group[i] = e;
+  }
+  const int last = n_experts > 0 ? (first[n_experts - 1] + (counts[n_experts - 1] + tile - 1) / tile * tile) / tile : 0;
+  for (int i = last + threadIdx.x; i < n_tiles; i += blockDim.x) tile_group[i] = -1;
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = ids[i];
+    if (e < n_experts) {
+      const int r = first[e] + pos[i];
+      pos[i] = r;
+      row_token[r] = i / top;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- gather
+// xp[r, :] = h[row_token[r], :], zeros for padding rows.
+template <typename T>
+__global__ void gather_kernel(T* __restrict__ xp, const T* __restrict__ h, int64_t ldh, const int* __restrict__ row_token,
+                              int K) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  const int r = blockIdx.x;
+  const int t = row_token[r];
+  T* dst = xp + (int64_t)r * K;
+  if (t < 0) {
+    for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = rb_from_float<T>(0.f);
+    return;
+  }
+  const T* src = h + (int64_t)t * ldh;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = src[k];
+}
+
+// ---------------------------------------------------------------- weighted sum
+// x[t, :] (+)= sum_j w[t, j] * (pos[t, j] >= 0 ? y[pos[t, j], :] : h[t, :]), the choices in their order.
+template <typename T>
+__global__ void combine_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ y, const T* __restrict__ h,
+                               int64_t ldh, const int* __restrict__ pos, const float* __restrict__ weights, int top, int E,
+                               int accumulate) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < E; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < top; ++j) {
+      const int r = pos[(int64_t)t * top + j];
+      const float w = weights[(int64_t)t * top + j];
+      const float v = r >= 0 ? y[(int64_t)r * E + c] : rb_to_float<T>(h[(int64_t)t * ldh + c]);
+      acc = fmaf(w, v, acc);
+    }
+    float* dst = x + (int64_t)t * ldx + c;
+    *dst = accumulate ? *dst + acc : acc;
+  }
+}
+
+// ---------------------------------------------------------------- grouped float32 product
+// C[rows, N] = act(A[rows, K] * W_g[N, K]^T) with g = tile_group[row / 64]: the plain tiled product of
+// gemm_simple.cu (one sequential float32 sum over k per output element) whose weight matrix changes from
+// one tile of 64 rows to the next.  Tiles without a group store zeros.
+constexpr int GM = 64, GN = 64, GK = 16;
+
+template <typename TA, typename TC>
+__global__ void __launch_bounds__(256) gemm_grouped_kernel(TC* __restrict__ C, int64_t ldc, const TA* __restrict__ A,
+                                                          int64_t lda, const TA* __restrict__ W, int64_t ldw,
+                                                          const int* __restrict__ tile_group, int N, int K,
+                                                          int square_relu) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  __shared__ float As[GK][GM + 1];
+  __shared__ float Ws[GK][GN + 1];
+  const int m0 = blockIdx.y * GM, n0 = blockIdx.x * GN;
+  const int g = tile_group[blockIdx.y];
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  if (g >= 0) {
+    const TA* Wg = W + (int64_t)g * N * ldw;
+    for (int k0 = 0; k0 < K; k0 += GK) {
+      for (int e = threadIdx.x; e < GM * GK; e += 256) {
+        const int r = e / GK, c = e % GK;
+        const int gn = n0 + r, gk = k0 + c;
+        As[c][r] = gk < K ? rb_to_float<TA>(A[(int64_t)(m0 + r) * lda + gk]) : 0.f;
+        Ws[c][r] = (gn < N && gk < K) ? rb_to_float<TA>(Wg[(int64_t)gn * ldw + gk]) : 0.f;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int kk = 0; kk < GK; ++kk) {
+        float a[4], w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+      }
+      __syncthreads();
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int gm = m0 + ty * 4 + i;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn >= N) continue;
+      float v = acc[i][j];
+      if (square_relu) { v = fmaxf(v, 0.f); v *= v; }
+      C[(int64_t)gm * ldc + gn] = rb_from_float<TC>(v);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- max(v, 0)^2, element by element
+template <typename T>
+__global__ void square_relu_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t n) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float v = fmaxf(rb_to_float<T>(in[i]), 0.f);
+    out[i] = rb_from_float<T>(v * v);
+  }
+}
+
+}  // namespace
+
+// ids, weights: [T, top].  h: the input rows (dtype h_dtype).  Wr: float32 [n, K]; correction: float32 [n] or null.
+// groups <= 1 or keep >= groups: every output can be chosen.
+RB_EXPORT int rb_route(int* ids, float* weights, const void* h, int64_t ldh, int h_dtype, const float* Wr,
+                       const float* correction, int T, int K, int n, int top, int groups, int keep, cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(K > 0 && n > 0 && top > 0 && top <= n, "rb_route: bad sizes K=%d outputs=%d top=%d", K, n, top);
+  RB_REQUIRE(groups <= 1 || n % groups == 0, "rb_route: %d outputs are not %d equal groups", n, groups);
+  if (groups < 1) groups = 1;
+  const int warps = 4;
+  const size_t smem = (size_t)warps * (2 * n + 2 * groups) * sizeof(float);
+  RB_REQUIRE(smem <= 48 * 1024, "rb_route: %d router outputs are more than a block's shared memory holds", n);
+  const int blocks = (T + warps - 1) / warps;
+  if (h_dtype == RB_F32)
+    RB_LAUNCH("route_kernel", (route_kernel<float>), blocks, warps * 32, smem, stream, ids, weights, (const float*)h, ldh, Wr, correction, T, K, n, top, groups, keep);
+  else if (h_dtype == RB_BF16)
+    RB_LAUNCH("route_kernel", (route_kernel<__nv_bfloat16>), blocks, warps * 32, smem, stream, ids, weights, (const __nv_bfloat16*)h, ldh, Wr, correction, T, K, n, top, groups, keep);
+  else
+    RB_FAIL("rb_route: unknown dtype %d", h_dtype);
+  RB_CHECK_LAUNCH("rb_route");
+  return 0;
+}
+
+// Tiles of rows the padded buffer needs at most for `pairs` pairs over n_experts experts.
+RB_EXPORT int rb_routed_tiles(int pairs, int n_experts, int tile) {
+  if (pairs <= 0 || tile <= 0) return 0;
+  const int used = pairs < n_experts ? pairs : n_experts;       // experts that can have rows
+  return (pairs + tile - 1) / tile + used;
+}
+
+RB_EXPORT int rb_routed_plan(int* pos, int* row_token, int* tile_group, const int* ids, int pairs, int top, int n_experts,
+                             int tile, int n_tiles, cudaStream_t stream) {
+  if (pairs == 0) return 0;
+  RB_REQUIRE(n_experts >= 0 && top > 0 && tile > 0 && n_tiles >= rb_routed_tiles(pairs, n_experts, tile),
+             "rb_routed_plan: %d tiles of %d rows for %d pairs over %d experts", n_tiles, tile, pairs, n_experts);
+  const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(int);
+  RB_REQUIRE(smem <= 48 * 1024, "rb_routed_plan: %d experts", n_experts);
+  RB_LAUNCH("plan_kernel", (plan_kernel), 1, 1024, smem, stream, pos, row_token, tile_group, ids, pairs, top, n_experts, tile, n_tiles);
+  RB_CHECK_LAUNCH("rb_routed_plan");
+  return 0;
+}
+
+RB_EXPORT int rb_routed_gather(void* xp, const void* h, int64_t ldh, int dtype, const int* row_token, int rows, int K,
+                               cudaStream_t stream) {
+  if (rows == 0) return 0;
+  const int threads = K >= 256 ? 256 : (K >= 128 ? 128 : 64);
+  if (dtype == RB_F32)
+    RB_LAUNCH("gather_kernel", (gather_kernel<float>), rows, threads, 0, stream, (float*)xp, (const float*)h, ldh, row_token, K);
+  else if (dtype == RB_BF16)
+    RB_LAUNCH("gather_kernel", (gather_kernel<__nv_bfloat16>), rows, threads, 0, stream, (__nv_bfloat16*)xp, (const __nv_bfloat16*)h, ldh, row_token, K);
+  else
+    RB_FAIL("rb_routed_gather: unknown dtype %d", dtype);
+  RB_CHECK_LAUNCH("rb_routed_gather");
+  return 0;
+}
+
+RB_EXPORT int rb_routed_combine(float* x, int64_t ldx, const float* y, const void* h, int64_t ldh, int h_dtype,
+                                const int* pos, const float* weights, int T, int top, int E, int accumulate,
+                                cudaStream_t stream) {
+  if (T == 0) return 0;
+  const int threads = E >= 256 ? 256 : (E >= 128 ? 128 : 64);
+  if (h_dtype == RB_F32)
+    RB_LAUNCH("combine_kernel", (combine_kernel<float>), T, threads, 0, stream, x, ldx, y, (const float*)h, ldh, pos, weights, top, E, accumulate);
+  else if (h_dtype == RB_BF16)
+    RB_LAUNCH("combine_kernel", (combine_kernel<__nv_bfloat16>), T, threads, 0, stream, x, ldx, y, (const __nv_bfloat16*)h, ldh, pos, weights, top, E, accumulate);
+  else
+    RB_FAIL("rb_routed_combine: unknown dtype %d", h_dtype);
+  RB_CHECK_LAUNCH("rb_routed_combine");
+  return 0;
+}
+
+// rows: a multiple of 64 (tile_group has rows / 64 entries).  W: [groups * N, K], one matrix per group.
+RB_EXPORT int rb_gemm_grouped_simple(void* C, int64_t ldc, int c_dtype, const void* A, int64_t lda, const void* W,
+                                     int64_t ldw, int a_dtype, const int* tile_group, int rows, int N, int K,
+                                     int square_relu, cudaStream_t stream) {
+  if (rows == 0 || N == 0) return 0;
+  RB_REQUIRE(rows % GM == 0 && N > 0 && K > 0, "rb_gemm_grouped_simple: %d rows (tiles of %d), N=%d K=%d", rows, GM, N, K);
+  const dim3 grid((N + GN - 1) / GN, rows / GM);
+  RB_REQUIRE(grid.y <= 65535, "rb_gemm_grouped_simple: %d rows are too many for one launch", rows);
+#define LAUNCH(TA, TC)                                                                                                 \
+  RB_LAUNCH("gemm_grouped_kernel", (gemm_grouped_kernel<TA, TC>), grid, 256, 0, stream, (TC*)C, ldc, (const TA*)A, lda, \
+            (const TA*)W, ldw, tile_group, N, K, square_relu)
+  if (a_dtype == RB_F32 && c_dtype == RB_F32) LAUNCH(float, float);
+  else if (a_dtype == RB_BF16 && c_dtype == RB_F32) LAUNCH(__nv_bfloat16, float);
+  else if (a_dtype == RB_BF16 && c_dtype == RB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else RB_FAIL("rb_gemm_grouped_simple: unsupported dtypes a=%d c=%d", a_dtype, c_dtype);
+#undef LAUNCH
+  RB_CHECK_LAUNCH("rb_gemm_grouped_simple");
+  return 0;
+}
+
+RB_EXPORT int rb_square_relu(void* out, const void* in, int dtype, long long n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  const long long most = (long long)rb_sm_count() * 16;
+  const int blocks = (int)((n + 255) / 256 < most ? (n + 255) / 256 : most);
+  if (dtype == RB_F32)
+    RB_LAUNCH("square_relu_kernel", (square_relu_kernel<float>), blocks, 256, 0, stream, (float*)out, (const float*)in, (int64_t)n);
+  else if (dtype == RB_BF16)
+    RB_LAUNCH("square_relu_kernel", (square_relu_kernel<__nv_bfloat16>), blocks, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)in, (int64_t)n);
+  else
+    RB_FAIL("rb_square_relu: unknown dtype %d", dtype);
+  RB_CHECK_LAUNCH("rb_square_relu");
+  return 0;
+}

@@ -124,8 +124,14 @@ class Model:
             x = ops.streams_expand(x, s)                                      # [T, s * E]: every stream starts as the embedding
         schedule, pending = self.spec.schedule, None
         taps = getattr(ctx, "layer_outputs", None)                            # a list: the residual sum after every run of a layer
+        # a schedule that adds the embedded rows again later keeps them (the blocks change x in place)
+        x0 = x.clone() if any(en.adds_embedding for en in schedule) else None
         for e, entry in enumerate(schedule):
             block = self.blocks[entry.layer]
+            if entry.adds_embedding:
+                if pending is not None:
+                    raise ValueError(f"schedule entry {e} adds the embedded rows, but the block before left its norm pending")
+                ops.add_rows(x, x0)
             if getattr(block, "chains_reads", False):
                 # a block that can hand the normed read of the next block's first sublayer on (see parts/block.py)
                 after = self.blocks[schedule[e + 1].layer] if e + 1 < len(schedule) else None
@@ -137,11 +143,17 @@ class Model:
             if not getattr(block, "chains_norms", False):
                 block.run(ctx, x, e)
                 pending = None
+                if taps is not None:
+                    taps.append(x.clone())
                 continue
-            # a block that can hand the rows of the next block's first norm on (see parts/block.py)
+            # a block that can hand the rows of the next block's first norm on (see parts/block.py); not to a run
+            # that adds the embedded rows first, whose norm sees another residual stream
             after = self.blocks[schedule[e + 1].layer] if e + 1 < len(schedule) else None
-            next_norm = after.first_norm() if getattr(after, "chains_norms", False) else None
+            hand_on = getattr(after, "chains_norms", False) and not schedule[e + 1].adds_embedding
+            next_norm = after.first_norm() if hand_on else None
             pending = block.run(ctx, x, e, pending=pending, next_norm=next_norm)
+            if taps is not None:
+                taps.append(ops.streams_sum(x, s) if s > 1 else x.clone())
         if meta.n_want == 0:
             return None
         rows = x if meta.want_every_row else ops.gather_rows(x, meta.want_rows)

@@ -27,16 +27,30 @@ _SIGNATURES = {
     "rb_streams_sum": [P, P, I, I, I, P],
     "rb_streams_max": [],
     "rb_streams_max_results": [],
-    "rb_norm_rotate_append": [P, P, L, I, P, P, F, P, F, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P],
-    "rb_head_gate": [P, P, P, L, I, I, I, I, I, P],
+    "rb_norm_rotate_append": [P, P, L, I, P, P, F, P, F, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P],
+    "rb_head_gate": [P, P, P, L, I, I, I, I, I, I, P],
     "rb_gated_act": [P, P, I, I, I, I, L, I, F, F, F, P],
-    "rb_conv_causal": [P, P, L, I, I, P, P, P, P, P, P, P, I, I, I, P],
+    "rb_conv_causal": [P, P, L, I, I, P, P, P, P, P, P, P, I, I, I, I, P],
+    "rb_conv_tail_update": [P, P, L, I, I, P, P, P, P, P, I, I, I, P],
+    "rb_delta_prepare": [P, L, P, L, I, I, P, P, P, P, P, I, I, I, I, F, F, P],
+    "rb_gated_delta": [P, P, L, P, P, P, P, P, P, P, I, I, I, I, I, P],
+    "rb_layernorm": [P, I, P, P, P, I, I, F, P],
+    "rb_add_rows": [P, P, ctypes.c_longlong, P],
+    "rb_route": [P, P, P, L, I, P, P, I, I, I, I, I, I, P],
+    "rb_routed_tiles": [I, I, I],
+    "rb_routed_plan": [P, P, P, P, I, I, I, I, I, P],
+    "rb_routed_gather": [P, P, L, I, P, I, I, P],
+    "rb_routed_combine": [P, L, P, P, L, I, P, P, I, I, I, I, P],
+    "rb_gemm_grouped_simple": [P, L, I, P, L, P, L, I, P, I, I, I, I, P],
+    "rb_square_relu": [P, P, I, ctypes.c_longlong, P],
+    "rb_gemm_tc_square_relu": [],
+    "rb_gemm_tc_grouped": [P],
     "rb_gated_step": [P, I, P, L, I, I, I, P, P, P, P, P, P, P, P, F, P, P, P, P, I, I, I, I, P],
     "rb_gated_step_max_rows": [],
     "rb_gated_scan": [P, I, P, P, P, P, P, F, P, L, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
     "rb_matrix_memory": [P, P, L, I, I, I, I, I, I, P, P, F, F, F, P, P, P, P, P, P, I, I, I, I, P],
     "rb_matrix_memory_lanes": [I],
-    "rb_head_norm_gate": [P, I, P, P, P, L, I, I, I, I, I, F, P],
+    "rb_head_norm_gate": [P, I, P, P, P, L, I, I, I, I, I, F, I, I, P],
     "rb_attention_simple": [P, P, I, P, P, P, I, I, P, P, I, I, I, I, F, I, P],
     "rb_sample": [P, P, L, I, I, P, P, P, P],
     "rb_sample_chunks": [I],

@@ -207,12 +207,34 @@ class CudaOps:
         self.lib.call("rb_rmsnorm", _ptr(out), _CODE[out.dtype], _ptr(x), _ptr(w), T, E, float(eps), self._stream())
         return out
 
+    def layernorm(self, x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float, out_dtype=None) -> torch.Tensor:
+        """(x - mean) / sqrt(variance + eps) * w + b per row, in float32; the result in the compute dtype."""
+        self._check(x, torch.float32, "layernorm input")
+        T, E = x.shape
+        out = torch.empty((T, E), dtype=out_dtype or self.dtype, device=self.device)
+        self.lib.call("rb_layernorm", _ptr(out), _CODE[out.dtype], _ptr(x), _ptr(w), _ptr(b), T, E, float(eps), self._stream())
+        return out
+
+    def add_rows(self, x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        """x += y, float32 rows of equal shape."""
+        self._check(x, torch.float32, "add_rows target")
+        self._check(y, torch.float32, "add_rows source")
+        if x.shape != y.shape:
+            raise KernelError(f"add_rows: shapes {tuple(x.shape)} and {tuple(y.shape)}")
+        self.lib.call("rb_add_rows", _ptr(x), _ptr(y), x.numel(), self._stream())
+        return x
+
     def linear(self, x, weight: LinearWeight, out_dtype=None, accumulate_into: Optional[torch.Tensor] = None,
-               scale: float = 1.0, then_norm: Optional[NormRequest] = None) -> torch.Tensor:
+               scale: float = 1.0, then_norm: Optional[NormRequest] = None, act: Optional[str] = None) -> torch.Tensor:
         """scale * x[T, in] * W[out, in]^T (the scale multiplies the finished float32 sums).  With
         ``accumulate_into`` (float32 [T, out]) the product is added to it in float32 and it is returned.
         ``x`` may be ``NormedRows``.  ``then_norm``: see ``NormRequest`` (granted for a few tokens, where
-        the product's parts along the inner dimension meet on chip)."""
+        the product's parts along the inner dimension meet on chip).  ``act`` "relu2": max(v, 0)^2 of the
+        finished float32 sums is stored (in the tensor-core product's epilogue, else by a kernel after it)."""
+        if act not in (None, "relu2"):
+            raise KernelError(f"linear: activation {act!r} is not built (only 'relu2')")
+        if act is not None and accumulate_into is not None:
+            raise KernelError("linear: an activation goes with a stored product, not an added one")
         pending = x if isinstance(x, NormedRows) else None
         if pending is not None:
             if self._takes_pending(pending, weight.w):
@@ -239,12 +261,16 @@ class CudaOps:
             # the norm's kernel also was the time in which the next product's first tiles of W arrived)
             if then_norm is not None and acc and splits >= 2 and T <= self.fold_norms_up_to and out.is_contiguous():
                 then_norm.result = self._leave_norm(out, then_norm, T, N)
+            if act is not None:
+                self.lib.call("rb_gemm_tc_square_relu", launches=0)
             self.lib.call("rb_gemm_tc", _ptr(out), out.stride(0), _CODE[out.dtype], _ptr(x), x.stride(0), T,
                           _ptr(weight.w), weight.w.stride(0), N, N, K, acc, 0, splits,
                           64 if 64 < T <= 256 else 0, float(scale), self._stream())
         else:
             self.lib.call("rb_gemm_simple", _ptr(out), out.stride(0), _CODE[out.dtype], _ptr(x), x.stride(0),
                           _ptr(weight.w), weight.w.stride(0), self.code, T, N, K, acc, float(scale), self._stream())
+            if act is not None:
+                self.lib.call("rb_square_relu", _ptr(out), _ptr(out), _CODE[out.dtype], out.numel(), self._stream())
         return out
 
     # ------------------------------------------------------------------ a norm between two products
@@ -529,10 +555,11 @@ class CudaOps:
         return -(-w // 16) * 16 if self.dtype == torch.bfloat16 else w
 
     def norm_rotate_append(self, proj: torch.Tensor, table, meta, view, n_heads: int, head_dim: int, value_dim: int,
-                           q_norm_w, k_norm_w, eps: float) -> torch.Tensor:
+                           q_norm_w, k_norm_w, eps: float, head_norm: bool = False) -> torch.Tensor:
         """From rows [q | k | v | ...] of the projections: q and k under an RMS norm over the whole
         projection (if weights are given), the first rot_dim values of every head turned by position, k and v
-        appended to the cache (rows ``view.head_dim`` wide, padded with zeros); returns q [T, H, view.head_dim]."""
+        appended to the cache (rows ``view.head_dim`` wide, padded with zeros); returns q [T, H, view.head_dim].
+        ``head_norm``: instead, every q and k head is divided by its own root mean square AFTER the rotation (no weights)."""
         self._check(proj, self.dtype, "norm_rotate_append projections")
         T, Dc, Kh = proj.shape[0], view.head_dim, view.n_kv_heads
         if table is None:
@@ -543,20 +570,21 @@ class CudaOps:
         self.lib.call("rb_norm_rotate_append", _ptr(q), _ptr(proj), proj.stride(0), self.code, _ptr(q_norm_w), _ptr(k_norm_w),
                       float(eps), _ptr(freq), float(magnitude), _ptr(meta.tok_pos), _ptr(meta.tok_slot), _ptr(view.k),
                       _ptr(view.v), _ptr(view.page_table), view.max_pages, view.page_size, T, n_heads, Kh, head_dim,
-                      value_dim, Dc, rot_dim, 1 if interleaved else 0, 1, self._stream())
+                      value_dim, Dc, rot_dim, 1 if interleaved else 0, 1, 1 if head_norm else 0, self._stream())
         return q
 
     def head_gate(self, a: torch.Tensor, proj: torch.Tensor, gate_column, n_heads: int, value_dim: int,
-                  cache_width: int) -> torch.Tensor:
+                  cache_width: int, per_value: bool = False) -> torch.Tensor:
         """[T, H * cache_width] -> [T, H * value_dim]: the padding dropped and head h multiplied by
-        sigmoid(proj[t, gate_column + h]) (no gate: ``gate_column`` None)."""
+        sigmoid(proj[t, gate_column + h]) (no gate: ``gate_column`` None); ``per_value``: value j of head h by
+        sigmoid(proj[t, gate_column + h * value_dim + j])."""
         if gate_column is None and value_dim == cache_width:
             return a
         T = a.shape[0]
         out = torch.empty((T, n_heads * value_dim), dtype=self.dtype, device=self.device)
         gate = c_void_p(proj.data_ptr() + gate_column * proj.element_size()) if gate_column is not None else c_void_p(0)
         self.lib.call("rb_head_gate", _ptr(out), _ptr(a), gate, proj.stride(0) if proj is not None else 0, self.code, T, n_heads, value_dim,
-                      cache_width, self._stream())
+                      cache_width, 1 if per_value else 0, self._stream())
         return out
 
     # ------------------------------------------------------------------ recurrent mixers
@@ -597,7 +625,7 @@ class CudaOps:
             return out
         u = torch.empty((T, W), dtype=torch.float32, device=self.device)
         self.lib.call("rb_conv_causal", _ptr(u), _ptr(proj), proj.stride(0), 0, F32, _ptr(f["x.b"]), _ptr(f["conv"]),
-                      _ptr(f["conv.b"]), _ptr(tail), _ptr(tok_first), _ptr(meta.tok_slot), _ptr(meta.tok_pos), T, W, K,
+                      _ptr(f["conv.b"]), _ptr(tail), _ptr(tok_first), _ptr(meta.tok_slot), _ptr(meta.tok_pos), T, W, K, 0,
                       self._stream())
         gates = torch.empty((T, B, 2 * Wb), dtype=torch.float32, device=self.device)
         self.lib.call("rb_gemm_simple_batched", _ptr(gates), gates.stride(0), F32, _ptr(u), u.stride(0), _ptr(p.w_gates), Wb,
@@ -623,7 +651,106 @@ class CudaOps:
                       n_seq, H, D, Dv, self._stream())
         out = torch.empty((T, H * Dv), dtype=self.dtype, device=self.device)
         self.lib.call("rb_head_norm_gate", _ptr(out), self.code, _ptr(o), _ptr(p.norm_w), _ptr(proj), proj.stride(0), F32,
-                      at["g"], T, H, Dv, float(p.norm_eps), self._stream())
+                      at["g"], T, H, Dv, float(p.norm_eps), 0, 0, self._stream())
+        return out
+
+    def gated_delta(self, proj: torch.Tensor, p, state, meta) -> torch.Tensor:
+        """The gated delta rule of ``parts.delta.GatedDeltaRule`` ``p`` on float32 rows [q | k | v | g | b | a] of its
+        stacked projection: short convolution and SiLU of q, k, v; unit vectors; gates; the recurrence; the heads'
+        outputs under their norm, weight and SiLU gate as [T, H * value_dim] in the compute dtype.  The sequences'
+        state (``state["S"]`` kept by value column, ``state["tail"]``) moves on."""
+        self._check(proj, torch.float32, "gated_delta projections")
+        T, H, G, D, Dv, K = proj.shape[0], p.n_heads, p.n_kv_heads, p.head_dim, p.value_dim, p.taps
+        C = 2 * G * D + H * Dv
+        at = p.offsets()
+        first, count, tok_first, n_runs = self._runs(meta)
+        tail = state.get("tail")
+        u = torch.empty((T, C), dtype=torch.float32, device=self.device)
+        self.lib.call("rb_conv_causal", _ptr(u), _ptr(proj), proj.stride(0), 0, F32, c_void_p(0), _ptr(p.conv_w), c_void_p(0),
+                      _ptr(tail), _ptr(tok_first), _ptr(meta.tok_slot), _ptr(meta.tok_pos), T, C, K, 1, self._stream())
+        gates = torch.empty((T * (2 * H + G),), dtype=torch.float32, device=self.device)
+        beta, decay, kq = gates[:T * H], gates[T * H:2 * T * H], gates[2 * T * H:]
+        self.lib.call("rb_delta_prepare", _ptr(u), u.stride(0), _ptr(proj), proj.stride(0), at["b"], at["a"], _ptr(p.a_log),
+                      _ptr(p.dt_bias), _ptr(beta), _ptr(decay), _ptr(kq), T, H, G, D, float(D) ** -0.5, float(p.unit_eps),
+                      self._stream())
+        o = torch.empty((T, H * Dv), dtype=torch.float32, device=self.device)
+        self.lib.call("rb_gated_delta", _ptr(o), _ptr(u), u.stride(0), _ptr(beta), _ptr(decay), _ptr(kq), _ptr(state["S"]),
+                      _ptr(first), _ptr(count), _ptr(meta.tok_slot), n_runs, H, G, D, Dv, self._stream())
+        if K > 1:
+            self.lib.call("rb_conv_tail_update", _ptr(tail), _ptr(proj), proj.stride(0), 0, F32, c_void_p(0), _ptr(first),
+                          _ptr(count), _ptr(meta.tok_slot), _ptr(meta.tok_pos), n_runs, C, K, self._stream())
+        out = torch.empty((T, H * Dv), dtype=self.dtype, device=self.device)
+        self.lib.call("rb_head_norm_gate", _ptr(out), self.code, _ptr(o), _ptr(p.norm_w), _ptr(proj), proj.stride(0), F32,
+                      at["g"], T, H, Dv, float(p.norm_eps), 1, 1, self._stream())
+        return out
+
+    # ------------------------------------------------------------------ routed experts
+    def route(self, h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int,
+              keep: int):
+        """(ids int32 [T, top], weights float32 [T, top]): softmax of the float32 router product over all outputs; the
+        ``top`` largest scores plus ``correction`` among the outputs of the ``keep`` best of ``groups`` equal groups;
+        the weights are the scores themselves."""
+        self._check(h, self.dtype, "route input")
+        T, K = h.shape
+        n = router.shape[0]
+        ids = torch.empty((T, top), dtype=torch.int32, device=self.device)
+        weights = torch.empty((T, top), dtype=torch.float32, device=self.device)
+        self.lib.call("rb_route", _ptr(ids), _ptr(weights), _ptr(h), h.stride(0), self.code, _ptr(router), _ptr(correction),
+                      T, K, n, int(top), int(groups), int(keep), self._stream())
+        return ids, weights
+
+    def routed_tile(self, pairs: int, n_experts: int, inner: int, width: int) -> int:
+        """Rows per tile of the buffer that holds a step's (token, choice) pairs sorted by expert."""
+        if not self._routed_on_tensor_cores(inner, width):
+            return 64            # the plain grouped product's tile
+        per = pairs / max(n_experts, 1)
+        return 16 if per <= 16 else 32 if per <= 32 else 64 if per <= 64 else 128
+
+    def _routed_on_tensor_cores(self, inner: int, width: int) -> bool:
+        return self.dtype == torch.bfloat16 and inner % 8 == 0 and width % 8 == 0
+
+    def routed_experts(self, h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_up: LinearWeight,
+                       w_down: LinearWeight, n_experts: int, inner: int, accumulate_into: Optional[torch.Tensor] = None):
+        """sum_j weights[t, j] * expert(ids[t, j])(h[t]) with expert e: W_down_e relu2(W_up_e h); ids >= n_experts are
+        identity experts (h[t] itself).  ``w_up``: [n_experts * inner, width], ``w_down``: [n_experts * width, inner].
+        Added to ``accumulate_into`` (float32), or returned as float32 rows."""
+        T, E = h.shape
+        top = ids.shape[1]
+        pairs = T * top
+        if accumulate_into is not None:
+            out, acc = accumulate_into, 1
+        else:
+            out, acc = torch.empty((T, E), dtype=torch.float32, device=self.device), 0
+        y = pos = None
+        if n_experts > 0:
+            tile = self.routed_tile(pairs, n_experts, inner, E)
+            n_tiles = self.lib.raw("rb_routed_tiles")(pairs, n_experts, tile)
+            rows = n_tiles * tile
+            plan = torch.empty((pairs + rows + n_tiles,), dtype=torch.int32, device=self.device)
+            pos, row_token, tile_group = plan[:pairs], plan[pairs:pairs + rows], plan[pairs + rows:]
+            self.lib.call("rb_routed_plan", _ptr(pos), _ptr(row_token), _ptr(tile_group), _ptr(ids), pairs, top, n_experts,
+                          tile, n_tiles, self._stream())
+            xp = torch.empty((rows, E), dtype=self.dtype, device=self.device)
+            self.lib.call("rb_routed_gather", _ptr(xp), _ptr(h), h.stride(0), self.code, _ptr(row_token), rows, E, self._stream())
+            mid = torch.empty((rows, inner), dtype=self.dtype, device=self.device)
+            y = torch.empty((rows, E), dtype=torch.float32, device=self.device)
+            if self._routed_on_tensor_cores(inner, E):
+                self.lib.call("rb_gemm_tc_square_relu", launches=0)
+                self.lib.call("rb_gemm_tc_grouped", _ptr(tile_group), launches=0)
+                self.lib.call("rb_gemm_tc", _ptr(mid), mid.stride(0), self.code, _ptr(xp), xp.stride(0), rows, _ptr(w_up.w),
+                              w_up.w.stride(0), n_experts * inner, inner, E, 0, 0, 1, tile, 1.0, self._stream())
+                self.lib.call("rb_gemm_tc_grouped", _ptr(tile_group), launches=0)
+                self.lib.call("rb_gemm_tc", _ptr(y), y.stride(0), F32, _ptr(mid), mid.stride(0), rows, _ptr(w_down.w),
+                              w_down.w.stride(0), n_experts * E, E, inner, 0, 0, 1, tile, 1.0, self._stream())
+            else:
+                self.lib.call("rb_gemm_grouped_simple", _ptr(mid), mid.stride(0), self.code, _ptr(xp), xp.stride(0), _ptr(w_up.w),
+                              w_up.w.stride(0), self.code, _ptr(tile_group), rows, inner, E, 1, self._stream())
+                self.lib.call("rb_gemm_grouped_simple", _ptr(y), y.stride(0), F32, _ptr(mid), mid.stride(0), _ptr(w_down.w),
+                              w_down.w.stride(0), self.code, _ptr(tile_group), rows, E, inner, 0, self._stream())
+        else:
+            pos = torch.full((pairs,), -1, dtype=torch.int32, device=self.device)
+        self.lib.call("rb_routed_combine", _ptr(out), out.stride(0), _ptr(y), _ptr(h), h.stride(0), self.code, _ptr(pos),
+                      _ptr(weights), T, top, E, acc, self._stream())
         return out
 
     def gather_rows(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

@@ -1,3 +1,4 @@
 """Architectures.  Importing this package registers them."""
 from . import llama  # noqa: F401
 from . import safuvik  # noqa: F401
+from . import vaderax  # noqa: F401

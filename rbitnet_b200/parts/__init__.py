@@ -1,12 +1,13 @@
 from .spec import PartSpec, BlockSpec, ScheduleEntry, ModelSpec
 from .base import Part, Norm, PositionEncoding, Mixer, FeedForward, Connection, CacheNeed, StateNeed
 from .registry import register_part, unregister_part, known_parts, build_part, build_block
-from .norm import RMSNorm
+from .norm import RMSNorm, LayerNorm
 from .position import RotaryEncoding, NoPositionEncoding
 from .attention import Attention
-from .feed_forward import GatedDense
+from .feed_forward import GatedDense, Dense, RoutedExperts
 from .block import PreNormBlock, StreamBlock
 from .recurrent import GatedLinearRecurrence, MatrixMemory
+from .delta import GatedDeltaRule
 from .parallel import ParallelMixers
 from .connection import ResidualConnection, HyperConnection
 
@@ -14,4 +15,5 @@ __all__ = ["PartSpec", "BlockSpec", "ScheduleEntry", "ModelSpec", "Part", "Norm"
            "Mixer", "FeedForward", "CacheNeed", "StateNeed", "register_part", "unregister_part",
            "known_parts", "build_part", "build_block", "RMSNorm", "RotaryEncoding", "NoPositionEncoding", "Attention",
            "GatedDense", "PreNormBlock", "StreamBlock", "Connection", "GatedLinearRecurrence", "MatrixMemory",
-           "ParallelMixers", "ResidualConnection", "HyperConnection"]
+           "ParallelMixers", "ResidualConnection", "HyperConnection", "LayerNorm", "Dense", "RoutedExperts",
+           "GatedDeltaRule"]

@@ -26,11 +26,13 @@ class PreNormBlock:
     def __init__(self, spec):
         self.spec = spec
         self._parts = build_parts(spec)
-        missing = [n for n in ("mixer", "feed_forward", "mixer_norm", "ffn_norm") if n not in self._parts]
+        missing = [n for n in ("mixer", "mixer_norm") if n not in self._parts]
         if missing:
             raise ValueError(f"a pre_norm block needs the parts {missing}")
-        self.mixer, self.feed_forward = self._parts["mixer"], self._parts["feed_forward"]
-        self.mixer_norm, self.ffn_norm = self._parts["mixer_norm"], self._parts["ffn_norm"]
+        if ("feed_forward" in self._parts) != ("ffn_norm" in self._parts):
+            raise ValueError("a pre_norm block has a feed-forward with its norm, or neither")
+        self.mixer, self.feed_forward = self._parts["mixer"], self._parts.get("feed_forward")
+        self.mixer_norm, self.ffn_norm = self._parts["mixer_norm"], self._parts.get("ffn_norm")
 
     def parts(self):
         return self._parts
@@ -60,6 +62,14 @@ class PreNormBlock:
         """``pending``: what the block before left for this block's first norm (or None).  Returns what
         it leaves for ``next_norm``, the first norm of the block after (or None)."""
         h = self._rows_for(ctx, self.mixer, self.mixer_norm, x, pending)
+        if self.feed_forward is None:
+            # a layer of a mixer alone: what the next block's first norm needs is asked of the mixer
+            request = self._request(ctx, next_norm, self.mixer)
+            if request is None:
+                self.mixer.forward(ctx, h, entry, accumulate_into=x)
+                return None
+            self.mixer.forward(ctx, h, entry, accumulate_into=x, then_norm=request)
+            return request.result
         request = self._request(ctx, self.ffn_norm, self.mixer)
         if request is None:
             self.mixer.forward(ctx, h, entry, accumulate_into=x)

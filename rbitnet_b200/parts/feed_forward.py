@@ -1,9 +1,12 @@
-"""Dense gated feed-forward: down( act(gate h) * (up h) ), act = SiLU, no bias
+"""Feed-forwards.  ``GatedDense``, the dense gated one: down( act(gate h) * (up h) ), act = SiLU, no bias
 (crates/bitnet-core/src/llama/model.rs:116-120, 296-306).  The activation and
 the product are float32 before any rounding to the compute dtype.
 
 ``activation`` "swish_limited": with g' = min(gate h, limit) and u' = clamp(up h, -limit, limit),
-the inner rows are g' * sigmoid(alpha g') * (u' + shift); alpha = 1.702 and shift = 1 unless given."""
+the inner rows are g' * sigmoid(alpha g') * (u' + shift); alpha = 1.702 and shift = 1 unless given.
+
+``Dense``: down(relu2(up h)), no gate.  ``RoutedExperts``: a router chooses a few of many small ``Dense`` ones
+(and identity experts) per token."""
 from __future__ import annotations
 
 import torch
@@ -49,4 +52,87 @@ class GatedDense(FeedForward):
             ctx.ops.linear(t, self.w_down, accumulate_into=accumulate_into, then_norm=then_norm)
 
 
+class Dense(FeedForward):
+    """down(act(up h)) without a gate and without biases; ``activation`` "relu2": max(z, 0)^2, taken of the
+    product's float32 sums before they are rounded to the compute dtype."""
+
+    def __init__(self, width: int, inner: int, activation: str = "relu2"):
+        if activation != "relu2":
+            raise ValueError(f"dense feed-forward: activation {activation!r} is not built (only 'relu2')")
+        self.width, self.inner, self.activation = int(width), int(inner), activation
+        self.w_up = self.w_down = None
+
+    def weight_shapes(self):
+        return {"up": ((self.inner, self.width), "matrix"), "down": ((self.width, self.inner), "matrix")}
+
+    def bind(self, weights, ops):
+        self.w_up = ops.prepare_linear([weights["up"]])
+        self.w_down = ops.prepare_linear([weights["down"]])
+
+    def forward(self, ctx, h, accumulate_into=None):
+        t = ctx.ops.linear(h, self.w_up, act=self.activation)
+        if accumulate_into is None:
+            return ctx.ops.linear(t, self.w_down, out_dtype=torch.float32)
+        ctx.ops.linear(t, self.w_down, accumulate_into=accumulate_into)
+
+
+class RoutedExperts(FeedForward):
+    """A mixture of ``n_experts`` small dense feed-forwards (down(relu2(up h)), no biases) of which every token
+    uses ``top``, plus ``n_identity`` identity experts whose result is the input row itself.
+
+    Router: z = Wr h in float32 over all n_experts + n_identity outputs, s = softmax(z).  The choice is made by
+    s + correction ("correction", one number per output), among the outputs of the ``keep`` best of ``groups`` equal
+    groups of neighbouring outputs (a group's score is its largest choice score; groups 0 or 1: no groups); the
+    chosen outputs' weights are their s, not renormalised.  The result is the weighted sum of the chosen experts'
+    results.  Weights: "router" [n_experts + n_identity, width], "correction" (``correction=False``: none), and
+    "e<i>.up" [inner, width], "e<i>.down" [width, inner] per expert."""
+
+    def __init__(self, width: int, inner: int, n_experts: int, top: int, n_identity: int = 0, groups: int = 0,
+                 keep: int = 0, correction: bool = True, activation: str = "relu2"):
+        if activation != "relu2":
+            raise ValueError(f"routed experts: activation {activation!r} is not built (only 'relu2')")
+        self.width, self.inner, self.n_experts, self.top = int(width), int(inner), int(n_experts), int(top)
+        self.n_identity, self.groups, self.keep = int(n_identity), int(groups or 0), int(keep or 0)
+        self.has_correction = bool(correction)
+        n = self.n_experts + self.n_identity
+        if not 1 <= self.top <= n:
+            raise ValueError(f"routed experts: {self.top} choices among {n} outputs")
+        if self.groups > 1:
+            if n % self.groups:
+                raise ValueError(f"routed experts: {n} router outputs are not {self.groups} equal groups")
+            if not 1 <= self.keep <= self.groups:
+                raise ValueError(f"routed experts: {self.keep} of {self.groups} groups kept")
+            if self.keep * (n // self.groups) < self.top:
+                raise ValueError(f"routed experts: {self.keep} groups of {n // self.groups} hold fewer than {self.top} outputs")
+        self.router = self.correction = self.w_up = self.w_down = None
+
+    def weight_shapes(self):
+        n = self.n_experts + self.n_identity
+        shapes = {"router": ((n, self.width), "matrix")}
+        if self.has_correction:
+            shapes["correction"] = ((n,), "matrix")
+        for e in range(self.n_experts):
+            shapes[f"e{e}.up"] = ((self.inner, self.width), "matrix")
+            shapes[f"e{e}.down"] = ((self.width, self.inner), "matrix")
+        return shapes
+
+    def bind(self, weights, ops):
+        # the router's product is float32 whatever the compute dtype
+        self.router = weights["router"].to(device=ops.device, dtype=torch.float32).contiguous()
+        self.correction = (weights["correction"].to(device=ops.device, dtype=torch.float32).contiguous()
+                           if self.has_correction else None)
+        if self.n_experts:
+            # the experts' matrices one below the other: [n_experts * inner, width] and [n_experts * width, inner]
+            self.w_up = ops.prepare_linear([weights[f"e{e}.up"] for e in range(self.n_experts)])
+            self.w_down = ops.prepare_linear([weights[f"e{e}.down"] for e in range(self.n_experts)])
+
+    def forward(self, ctx, h, accumulate_into=None):
+        ops = ctx.ops
+        ids, weights = ops.route(h, self.router, self.correction, self.top, self.groups, self.keep)
+        return ops.routed_experts(h, ids, weights, self.w_up, self.w_down, self.n_experts, self.inner,
+                                  accumulate_into=accumulate_into)
+
+
 register_part("feed_forward", "gated_dense", GatedDense)
+register_part("feed_forward", "dense", Dense)
+register_part("feed_forward", "routed_experts", RoutedExperts)

@@ -1,5 +1,6 @@
-"""RMSNorm: y = x * w / sqrt(mean(x^2) + eps), all in float32
-(crates/bitnet-core/src/llama/model.rs:93-100).  The weight multiplies directly (no 1+w)."""
+"""Norms over the model width.  RMSNorm: y = x * w / sqrt(mean(x^2) + eps), all in float32
+(crates/bitnet-core/src/llama/model.rs:93-100).  The weight multiplies directly (no 1+w).
+LayerNorm: the mean taken off first, and a bias added."""
 from __future__ import annotations
 
 import torch
@@ -30,4 +31,27 @@ class RMSNorm(Norm):
         return make(self.weight, self.eps) if make is not None else None
 
 
+class LayerNorm(Norm):
+    """y = (x - mean(x)) / sqrt(var(x) + eps) * w + b over the width, var the mean of the squared deviations; all in
+    float32.  Weights "weight" and "bias" (``bias=False``: none)."""
+
+    def __init__(self, width: int, eps: float, bias: bool = True):
+        self.width, self.eps, self.has_bias = int(width), float(eps), bool(bias)
+        self.weight = self.bias = None
+
+    def weight_shapes(self):
+        shapes = {"weight": ((self.width,), "norm")}
+        if self.has_bias:
+            shapes["bias"] = ((self.width,), "matrix")
+        return shapes
+
+    def bind(self, weights, ops):
+        self.weight = weights["weight"].to(torch.float32).contiguous()
+        self.bias = weights["bias"].to(torch.float32).contiguous() if self.has_bias else None
+
+    def forward(self, ctx, x):
+        return ctx.ops.layernorm(x, self.weight, self.bias, self.eps)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)

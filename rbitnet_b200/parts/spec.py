@@ -70,9 +70,13 @@ class BlockSpec:
 @dataclass
 class ScheduleEntry:
     """One run of a layer.  ``reads_cache_of`` names an EARLIER entry of the schedule
-    whose keys and values this run reads instead of writing its own."""
+    whose keys and values this run reads instead of writing its own.  A layer may run several times
+    (a span of layers that is looped): every run has its own cache and state."""
     layer: int
     reads_cache_of: Optional[int] = None
+    #: the embedded rows (the residual stream as it was before the first layer) are added to the residual
+    #: stream right before this run
+    adds_embedding: bool = False
 
 
 @dataclass

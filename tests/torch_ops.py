@@ -56,8 +56,20 @@ class TorchOps:
         s = (x * x).sum(-1, keepdim=True) / x.shape[-1]
         return (x * w * (1.0 / torch.sqrt(s + eps))).to(out_dtype or self.dtype)
 
-    def linear(self, x, weight, out_dtype=None, accumulate_into=None, scale=1.0):
+    def layernorm(self, x, w, b, eps, out_dtype=None):
+        mu = x.mean(-1, keepdim=True)
+        var = ((x - mu) ** 2).mean(-1, keepdim=True)
+        y = (x - mu) / torch.sqrt(var + eps) * w
+        return (y + b if b is not None else y).to(out_dtype or self.dtype)
+
+    def add_rows(self, x, y):
+        x += y
+        return x
+
+    def linear(self, x, weight, out_dtype=None, accumulate_into=None, scale=1.0, act=None):
         y = x.to(torch.float32) @ weight.w.to(torch.float32).T * scale
+        if act == "relu2":
+            y = torch.clamp(y, min=0.0) ** 2
         if accumulate_into is not None:
             accumulate_into += y
             return accumulate_into
@@ -110,7 +122,8 @@ class TorchOps:
     def cache_head_width(self, head_dim, value_dim):
         return max(head_dim, value_dim)
 
-    def norm_rotate_append(self, proj, table, meta, view, n_heads, head_dim, value_dim, q_norm_w, k_norm_w, eps):
+    def norm_rotate_append(self, proj, table, meta, view, n_heads, head_dim, value_dim, q_norm_w, k_norm_w, eps,
+                           head_norm=False):
         T, H, D, Dv, Kh, Dc = proj.shape[0], n_heads, head_dim, value_dim, view.n_kv_heads, view.head_dim
         x = proj.to(torch.float32)
         q, k, v = x[:, :H * D], x[:, H * D:(H + Kh) * D], x[:, (H + Kh) * D:(H + Kh) * D + Kh * Dv]
@@ -129,6 +142,9 @@ class TorchOps:
                 else:
                     a, b = t_[..., :rot // 2].clone(), t_[..., rot // 2:rot].clone()
                     t_[..., :rot // 2], t_[..., rot // 2:rot] = a * c - b * s_, b * c + a * s_
+        if head_norm:
+            q = q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps)
+            k = k / torch.sqrt((k * k).mean(-1, keepdim=True) + eps)
         qo = torch.zeros(T, H, Dc)
         qo[..., :D] = q
         for t in range(T):
@@ -140,10 +156,13 @@ class TorchOps:
             view.v[page, :, p % view.page_size, :Dv] = v[t].to(view.v.dtype)
         return qo.to(self.dtype)
 
-    def head_gate(self, a, proj, gate_column, n_heads, value_dim, cache_width):
+    def head_gate(self, a, proj, gate_column, n_heads, value_dim, cache_width, per_value=False):
         T = a.shape[0]
         out = a.to(torch.float32).view(T, n_heads, cache_width)[:, :, :value_dim]
-        if gate_column is not None:
+        if gate_column is not None and per_value:
+            g = proj[:, gate_column:gate_column + n_heads * value_dim].to(torch.float32)
+            out = out * torch.sigmoid(g).view(T, n_heads, value_dim)
+        elif gate_column is not None:
             out = out * torch.sigmoid(proj[:, gate_column:gate_column + n_heads].to(torch.float32))[:, :, None]
         return out.reshape(T, n_heads * value_dim).to(self.dtype)
 
@@ -204,6 +223,70 @@ class TorchOps:
         o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + p.norm_eps)
         g = torch.sigmoid(x[:, at["g"]:at["g"] + H * Dv])
         return (o.reshape(T, H * Dv) * p.norm_w * g).to(self.dtype)
+
+    def gated_delta(self, proj, p, state, meta):
+        H, G, D, Dv, K = p.n_heads, p.n_kv_heads, p.head_dim, p.value_dim, p.taps
+        C = 2 * G * D + H * Dv
+        at = p.offsets()
+        x = proj.float()
+        T = x.shape[0]
+        o = torch.zeros(T, H, Dv)
+        share = torch.arange(H) // (H // G)
+        for first, n, slot in self._runs(meta):
+            xin = x[first:first + n, :C]
+            old = state["tail"][slot][1:] if K > 1 else torch.zeros(0, C)      # this stand-in keeps the last K-1 inputs in rows 1..
+            hist = torch.cat([old, xin], dim=0)
+            S = state["S"][slot].clone()                                        # [H, Dv, D]
+            for t in range(n):
+                u = (hist[t:t + K] * p.conv_w.T).sum(0)
+                u = u / (1.0 + torch.exp(-u))
+                q, k, v = u[:G * D].view(G, D), u[G * D:2 * G * D].view(G, D), u[2 * G * D:].view(H, Dv)
+                q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + p.unit_eps) * D ** -0.5
+                k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + p.unit_eps)
+                q, k = q[share], k[share]
+                row = x[first + t]
+                beta = torch.sigmoid(row[at["b"]:at["b"] + H])
+                g = torch.exp(-torch.exp(p.a_log) * torch.nn.functional.softplus(row[at["a"]:at["a"] + H] + p.dt_bias))
+                S = S * g[:, None, None]
+                w = beta[:, None] * (v - torch.einsum("hvd,hd->hv", S, k))
+                S = S + w[:, :, None] * k[:, None, :]
+                o[first + t] = torch.einsum("hvd,hd->hv", S, q)
+            state["S"][slot] = S
+            if K > 1:
+                state["tail"][slot][1:] = hist[n:n + K - 1]
+        o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + p.norm_eps) * p.norm_w
+        gate = x[:, at["g"]:at["g"] + H * Dv]
+        return (o.reshape(T, H * Dv) * (gate / (1.0 + torch.exp(-gate)))).to(self.dtype)
+
+    # ---- routed experts
+    def route(self, h, router, correction, top, groups, keep):
+        s = torch.softmax(h.to(torch.float32) @ router.T, dim=-1)
+        choice = s + correction if correction is not None else s.clone()
+        if groups > 1 and keep < groups:
+            per = s.shape[1] // groups
+            best = choice.view(-1, groups, per).max(-1).values
+            kept = torch.zeros_like(best, dtype=torch.bool).scatter_(1, best.topk(keep, dim=-1).indices, True)
+            choice = choice.masked_fill(~kept.repeat_interleave(per, dim=1), -math.inf)
+        ids = choice.topk(top, dim=-1).indices
+        return ids.to(torch.int32), s.gather(1, ids)
+
+    def routed_experts(self, h, ids, weights, w_up, w_down, n_experts, inner, accumulate_into=None):
+        T, E = h.shape
+        x = h.to(torch.float32)
+        out = torch.zeros(T, E)
+        for t in range(T):
+            for e, w in zip(ids[t].tolist(), weights[t]):
+                if e >= n_experts:
+                    out[t] += w * x[t]
+                    continue
+                up = w_up.w[e * inner:(e + 1) * inner].to(torch.float32)
+                down = w_down.w[e * E:(e + 1) * E].to(torch.float32)
+                mid = (torch.clamp(up @ x[t], min=0.0) ** 2).to(self.dtype).to(torch.float32)
+                out[t] += w * (down @ mid)
+        if accumulate_into is not None:
+            accumulate_into += out
+            return accumulate_into
+        return out
 
     def project_rotate_append(self, h, weight, rotary, meta, view, n_heads):
         return self.rotate_append(self.linear(h, weight), rotary, meta, view, n_heads)
