@@ -508,17 +508,41 @@ def _llama_like(width, heads, kv, dim, ff, layers, vocab=32000):
                 rms_norm_eps=1e-6, max_position_embeddings=8192, tie_word_embeddings=False, hidden_act="silu")
 
 
+def _vaderax_shape(width, heads, kv, dim, delta_heads, delta_kv, delta_dim, delta_vdim, ff, experts, top, expert_ff, layers,
+                   vocab=32000):
+    """Layer sizes in the manner of a real model: of every three layers two are delta rules and one is attention; the first
+    layer's feed-forward is dense, the others route `top` of `experts` experts (whose inner sizes add up to the dense
+    one's: top * expert_ff = ff) with two identity experts, half of eight groups kept; the two middle layers run twice."""
+    att = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "rot": {"base": 10000.0, "dims": dim // 2}}
+    delta = {"heads": delta_heads, "kv_heads": delta_kv, "dim": delta_dim, "vdim": delta_vdim, "conv": 4}
+    routed = {"kind": "moe", "expert": {"ff": expert_ff},
+              "router": {"experts": experts, "identity": 2, "top": top, "groups": {"count": (experts + 2) // 2 if (experts + 2) % 8 else 8,
+                                                                               "keep": ((experts + 2) // 2 if (experts + 2) % 8 else 8) // 2}}}
+    ls = []
+    for i in range(layers):
+        ls.append({"type": "attention" if i % 3 == 2 else "delta", "mixer": att if i % 3 == 2 else delta,
+                   "mlp": {"kind": "dense", "ff": ff} if i == 0 else routed})
+    cfg = {"architecture": "Vaderax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+           "max_positions": 8192, "layers": ls}
+    if layers >= 4:
+        cfg["loop"] = {"start": 1, "stop": 3, "times": 2}
+    return cfg
+
+
 DESIGN_SIZES = {
-    # name: (Safuvik configuration, Llama configuration of equal width, layers, feed-forward and attention heads)
+    # name: (the design's configuration, Llama configuration of equal width, layers, feed-forward and attention heads)
     "w2048": (_safuvik_shape(2048, 16, 4, 128, 64, 1024, 16, 8, 128, 256, 5632, 6), _llama_like(2048, 16, 4, 128, 5632, 6)),
     "w4096": (_safuvik_shape(4096, 32, 8, 128, 128, 1024, 16, 8, 256, 512, 14336, 3), _llama_like(4096, 32, 8, 128, 14336, 3)),
+    # Vaderax: 4 stored layers of which two run twice (6 runs) beside 6 Llama layers; 3 layers beside 3
+    "vaderax_w2048": (_vaderax_shape(2048, 16, 4, 128, 16, 8, 128, 128, 5632, 30, 4, 1408, 4), _llama_like(2048, 16, 4, 128, 5632, 6)),
+    "vaderax_w4096": (_vaderax_shape(4096, 32, 8, 128, 32, 16, 128, 128, 14336, 62, 8, 1792, 3), _llama_like(4096, 32, 8, 128, 14336, 3)),
 }
 
 
 class DesignTimer(KernelTimer):
     """KernelTimer with the operations of the recurrent mixers and of the residual streams."""
     OPS = KernelTimer.OPS + ("stream_step", "normed_mean", "streams_expand", "streams_sum", "norm_rotate_append", "head_gate",
-                             "gated_recurrence", "matrix_memory")
+                             "gated_recurrence", "matrix_memory", "layernorm", "add_rows", "gated_delta", "route", "routed_experts")
 
     @staticmethod
     def _describe(name, a, kw, sync=True):
@@ -548,6 +572,24 @@ class DesignTimer(KernelTimer):
             T = proj.shape[0]
             return (f"matrix memory: recurrence, head norm and gate [{T} rows, {p.n_heads} heads of {p.head_dim}x{p.value_dim}]",
                     el(proj) + T * p.n_heads * p.value_dim * 2, 0.0)
+        if name == "gated_delta":
+            proj, p = a[0], a[1]
+            T = proj.shape[0]
+            return (f"delta rule: convolution, unit vectors, gates, recurrence, head norm and gate [{T} rows, {p.n_heads} heads of "
+                    f"{p.head_dim}x{p.value_dim}]", el(proj) + T * p.n_heads * p.value_dim * 2,
+                    0.0)
+        if name == "route":
+            h, router = a[0], a[1]
+            return f"router [{h.shape[0]} rows, {router.shape[0]} outputs]", el(h) + el(router), 0.0
+        if name == "routed_experts":
+            h, ids, w_up, w_down, inner = a[0], a[1], a[3], a[4], a[6]
+            T, E = h.shape
+            pairs = T * ids.shape[1]
+            used = min(1.0, pairs / max(a[5], 1))          # the share of the experts' matrices a step has to read at least
+            return (f"routed experts: plan, gather, two grouped products, weighted sum [{T} rows, {ids.shape[1]} of {a[5]} experts of {inner}]",
+                    int(used * (el(w_up.w) + el(w_down.w))) + pairs * (E * 2 + E * 4) + 2 * T * E * 4, 4.0 * pairs * E * inner)
+        if name in ("layernorm", "add_rows"):
+            return f"{name} [{a[0].shape[0]} rows]", (2 if name == "layernorm" else 3) * el(a[0]), 0.0
         if name in ("normed_mean", "streams_expand", "streams_sum"):
             t = a[0][0] if name == "normed_mean" else a[0]
             return f"{name} [{t.shape[0]} rows]", 3 * el(t), 0.0
@@ -561,9 +603,10 @@ def run_design(name, args):
     from rbitnet_b200 import Engine, StepEntry
     pk = peaks()
     steps, warmup = max(1, args.steps), max(3, args.warmup)
-    out = {"design": "Safuvik beside Llama", "size": name, "peaks": pk, "dtype": "bf16", "data": "synthetic (random weights)",
+    design = str(DESIGN_SIZES[name][0].get("architecture", "design"))
+    out = {"design": f"{design} beside Llama", "size": name, "peaks": pk, "dtype": "bf16", "data": "synthetic (random weights)",
            "batch": args.batch, "context": args.context, "prefill_tokens": args.prefill_tokens, "models": {}}
-    for label, cfg in zip(("safuvik", "llama"), DESIGN_SIZES[name]):
+    for label, cfg in zip((design.lower(), "llama"), DESIGN_SIZES[name]):
         room = steps + warmup + 16
         ctx = args.context
         max_tokens = max(args.batch * (-(-(ctx + room) // 64) * 64), args.prefill_tokens + 64) + 64 * 8
@@ -573,12 +616,12 @@ def run_design(name, args):
                 pool.normal_(0.0, 1.0)
         torch.cuda.synchronize()
         if args.timeline:
-            if label == "safuvik":
+            if label != "llama":
                 print_timeline(engine, args.batch, ctx)
             continue
         pf_ms = time_prefill(engine, args.prefill_tokens)
         ms, launches, _ = time_decode(engine, args.batch, ctx, steps, warmup)
-        nbytes = decode_bytes(engine, args.batch, ctx if label == "llama" else min(ctx, 1024))
+        nbytes = decode_bytes(engine, args.batch, min(ctx, 1024) if label == "safuvik" else ctx)
         rec = {"layers": len(engine.spec.layers), "width": engine.spec.width,
                "prefill_ms": round(pf_ms, 3), "prefill_tokens_per_s": round(args.prefill_tokens / pf_ms * 1e3, 1),
                "decode_ms_per_step": round(ms, 4), "decode_tokens_per_s": round(args.batch / ms * 1e3, 1),
@@ -642,7 +685,7 @@ def main():
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="run one of the other generation workloads end to end instead (one short line)")
     ap.add_argument("--design", default=None, choices=sorted(DESIGN_SIZES),
-                    help="instead of the headline: prefill and decode of the Safuvik design beside the Llama decoder of "
+                    help="instead of the headline: prefill and decode of another design (Safuvik; vaderax_*: Vaderax) beside the Llama decoder of "
                          "equal size at these layer sizes (uses --batch, --context, --prefill-tokens, --steps)")
     args = ap.parse_args()
 

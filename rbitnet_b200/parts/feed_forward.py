@@ -102,8 +102,6 @@ class RoutedExperts(FeedForward):
                 raise ValueError(f"routed experts: {n} router outputs are not {self.groups} equal groups")
             if not 1 <= self.keep <= self.groups:
                 raise ValueError(f"routed experts: {self.keep} of {self.groups} groups kept")
-            if self.keep * (n // self.groups) < self.top:
-                raise ValueError(f"routed experts: {self.keep} groups of {n // self.groups} hold fewer than {self.top} outputs")
         self.router = self.correction = self.w_up = self.w_down = None
 
     def weight_shapes(self):
