@@ -19,30 +19,74 @@
 namespace {
 
 // ---------------------------------------------------------------- router
-// One warp per token, with 2 n + 2 groups floats of shared memory.
+// A block of 8 warps takes TB tokens (up to 8).  Its warps share the router's outputs: a warp makes output e for all
+// of the block's tokens at once, so that a row of Wr is read once per block (lanes stride over k four values at a
+// time; a token's sum is the lanes' partial sums added in a fixed tree, whatever other tokens the block holds).  Then
+// warp w makes the choice of token w.  Shared memory: per token 2 n + 2 groups floats.
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+  const float4 f = *reinterpret_cast<const float4*>(p);
+  v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+
+constexpr int ROUTE_TB = 8;
+
 template <typename TI>
-__global__ void __launch_bounds__(128) route_kernel(int* __restrict__ ids, float* __restrict__ weights,
+__global__ void __launch_bounds__(256) route_kernel(int* __restrict__ ids, float* __restrict__ weights,
                                                     const TI* __restrict__ h, int64_t ldh,
                                                     const float* __restrict__ Wr, const float* __restrict__ correction,
-                                                    int T, int K, int n, int top, int groups, int keep) {
+                                                    int T, int K, int n, int top, int groups, int keep, int TB, int vec) {
   rb_pdl_launch_dependents();
   extern __shared__ float s_route[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-  float* z = s_route + (size_t)warp * (2 * n + 2 * groups);     // scores, choice scores, group scores, kept groups
+  const int per_token = 2 * n + 2 * groups;
+  const int t0 = blockIdx.x * TB;
+  const int nt = min(TB, T - t0);
+  rb_pdl_wait();
+  for (int e = warp; e < n; e += 8) {
+    const float* w = Wr + (int64_t)e * K;
+    float acc[ROUTE_TB];
+#pragma unroll
+    for (int j = 0; j < ROUTE_TB; ++j) acc[j] = 0.f;
+    if (vec) {
+      for (int k = lane * 4; k < K; k += 128) {
+        float wv[4];
+        load4(w + k, wv);
+#pragma unroll
+        for (int j = 0; j < ROUTE_TB; ++j) {
+          if (j < nt) {
+            float hv[4];
+            load4(h + (int64_t)(t0 + j) * ldh + k, hv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[j] = fmaf(hv[i], wv[i], acc[j]);
+          }
+        }
+      }
+    } else {
+      for (int k = lane; k < K; k += 32) {
+        const float wk = w[k];
+#pragma unroll
+        for (int j = 0; j < ROUTE_TB; ++j)
+          if (j < nt) acc[j] = fmaf(rb_to_float<TI>(h[(int64_t)(t0 + j) * ldh + k]), wk, acc[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < ROUTE_TB; ++j) {
+      const float v = rb_warp_sum(acc[j]);
+      if (lane == 0 && j < nt) s_route[(size_t)j * per_token + e] = v;
+    }
+  }
+  __syncthreads();
+  if (warp >= nt) return;
+  const int t = t0 + warp;
+  float* z = s_route + (size_t)warp * per_token;     // scores, choice scores, group scores, kept groups
   float* choice = z + n;
   float* gscore = choice + n;
-  rb_pdl_wait();
-  if (t >= T) return;
-  const TI* row = h + (int64_t)t * ldh;
-  for (int e = 0; e < n; ++e) {
-    const float* w = Wr + (int64_t)e * K;
-    float acc = 0.f;
-    for (int k = lane; k < K; k += 32) acc = fmaf(rb_to_float<TI>(row[k]), w[k], acc);
-    acc = rb_warp_sum(acc);
-    if (lane == 0) z[e] = acc;
-  }
-  __syncwarp();
   float m = -INFINITY;
   for (int e = lane; e < n; e += 32) m = fmaxf(m, z[e]);
   m = rb_warp_max(m);
@@ -57,7 +101,7 @@ __global__ void __launch_bounds__(128) route_kernel(int* __restrict__ ids, float
     choice[e] = s + (correction != nullptr ? correction[e] : 0.f);
   }
   __syncwarp();
-  // the largest value of v[0..count) that is not -inf-marked, lowest index on ties; every lane gets the index
+  // the largest value of v[0..count) that is not -inf, lowest index on ties; every lane gets the index
   auto arg_max = [&](const float* v, int count) {
     float best = -INFINITY;
     int at = 0x7fffffff;
@@ -274,14 +318,17 @@ RB_EXPORT int rb_route(int* ids, float* weights, const void* h, int64_t ldh, int
   RB_REQUIRE(K > 0 && n > 0 && top > 0 && top <= n, "rb_route: bad sizes K=%d outputs=%d top=%d", K, n, top);
   RB_REQUIRE(groups <= 1 || n % groups == 0, "rb_route: %d outputs are not %d equal groups", n, groups);
   if (groups < 1) groups = 1;
-  const int warps = 4;
-  const size_t smem = (size_t)warps * (2 * n + 2 * groups) * sizeof(float);
+  // few tokens: a block each, so that the rows of Wr are read by many SMs at once; many: eight tokens a block
+  const int TB = T >= 64 ? ROUTE_TB : 1;
+  const size_t smem = (size_t)TB * (2 * n + 2 * groups) * sizeof(float);
   RB_REQUIRE(smem <= 48 * 1024, "rb_route: %d router outputs are more than a block's shared memory holds", n);
-  const int blocks = (T + warps - 1) / warps;
+  const int blocks = (T + TB - 1) / TB;
+  const int elem = h_dtype == RB_F32 ? 4 : 2;
+  const int vec = K % 4 == 0 && ldh % 4 == 0 && (uintptr_t)h % (4 * elem) == 0 && (uintptr_t)Wr % 16 == 0;
   if (h_dtype == RB_F32)
-    RB_LAUNCH("route_kernel", (route_kernel<float>), blocks, warps * 32, smem, stream, ids, weights, (const float*)h, ldh, Wr, correction, T, K, n, top, groups, keep);
+    RB_LAUNCH("route_kernel", (route_kernel<float>), blocks, 256, smem, stream, ids, weights, (const float*)h, ldh, Wr, correction, T, K, n, top, groups, keep, TB, vec);
   else if (h_dtype == RB_BF16)
-    RB_LAUNCH("route_kernel", (route_kernel<__nv_bfloat16>), blocks, warps * 32, smem, stream, ids, weights, (const __nv_bfloat16*)h, ldh, Wr, correction, T, K, n, top, groups, keep);
+    RB_LAUNCH("route_kernel", (route_kernel<__nv_bfloat16>), blocks, 256, smem, stream, ids, weights, (const __nv_bfloat16*)h, ldh, Wr, correction, T, K, n, top, groups, keep, TB, vec);
   else
     RB_FAIL("rb_route: unknown dtype %d", h_dtype);
   RB_CHECK_LAUNCH("rb_route");
