@@ -254,10 +254,67 @@ __global__ void __launch_bounds__(256) layernorm_kernel(TO* __restrict__ out, co
   for (int e = threadIdx.x; e < E; e += blockDim.x) dst[e] = rb_from_float<TO>((row[e] - mean) * r * w[e] + (b != nullptr ? b[e] : 0.f));
 }
 
+// The same with the row held in registers (NV groups of four values a thread, 16-byte accesses): the row is read once.
+template <typename TO, int NV>
+__global__ void __launch_bounds__(256) layernorm_reg_kernel(TO* __restrict__ out, const float* __restrict__ x,
+                                                            const float* __restrict__ w, const float* __restrict__ b, int E,
+                                                            float eps) {
+  rb_pdl_launch_dependents();
+  __shared__ float scratch[33];
+  rb_pdl_wait();
+  const float4* row = reinterpret_cast<const float4*>(x + (int64_t)blockIdx.x * E);
+  const int E4 = E >> 2;
+  float4 v[NV];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int e = threadIdx.x + i * 256;
+    v[i] = e < E4 ? row[e] : make_float4(0.f, 0.f, 0.f, 0.f);
+    s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  }
+  const float mean = rb_block_sum(s, scratch) / (float)E;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int e = threadIdx.x + i * 256;
+    if (e < E4) {
+      v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+      q = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, q))));
+    }
+  }
+  const float r = 1.0f / sqrtf(rb_block_sum(q, scratch) / (float)E + eps);
+  TO* dst = out + (int64_t)blockIdx.x * E;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int e = threadIdx.x + i * 256;
+    if (e < E4) {
+      const float4 ww = reinterpret_cast<const float4*>(w)[e];
+      const float4 bb = b != nullptr ? reinterpret_cast<const float4*>(b)[e] : make_float4(0.f, 0.f, 0.f, 0.f);
+      store4<TO>(dst + 4 * e, v[i].x * r * ww.x + bb.x, v[i].y * r * ww.y + bb.y, v[i].z * r * ww.z + bb.z, v[i].w * r * ww.w + bb.w);
+    }
+  }
+}
+
+template <typename TO>
+int launch_layernorm_reg(TO* out, const float* x, const float* w, const float* b, int T, int E, float eps, cudaStream_t stream) {
+  const int groups = (E / 4 + 255) / 256;
+  if (groups <= 1) RB_LAUNCH("layernorm_reg_kernel", (layernorm_reg_kernel<TO, 1>), T, 256, 0, stream, out, x, w, b, E, eps);
+  else if (groups <= 2) RB_LAUNCH("layernorm_reg_kernel", (layernorm_reg_kernel<TO, 2>), T, 256, 0, stream, out, x, w, b, E, eps);
+  else if (groups <= 4) RB_LAUNCH("layernorm_reg_kernel", (layernorm_reg_kernel<TO, 4>), T, 256, 0, stream, out, x, w, b, E, eps);
+  else RB_LAUNCH("layernorm_reg_kernel", (layernorm_reg_kernel<TO, 8>), T, 256, 0, stream, out, x, w, b, E, eps);
+  RB_CHECK_LAUNCH("rb_layernorm");
+  return 0;
+}
+
 RB_EXPORT int rb_layernorm(void* out, int out_dtype, const float* x, const float* w, const float* b, int T, int E, float eps,
                            cudaStream_t stream) {
   if (T == 0) return 0;
   RB_REQUIRE(E > 0, "rb_layernorm: width %d", E);
+  if (E % 4 == 0 && E >= 512 && E <= 8192 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)b % 16 == 0 &&
+      (uintptr_t)out % 16 == 0) {
+    if (out_dtype == RB_F32) return launch_layernorm_reg<float>((float*)out, x, w, b, T, E, eps, stream);
+    if (out_dtype == RB_BF16) return launch_layernorm_reg<__nv_bfloat16>((__nv_bfloat16*)out, x, w, b, T, E, eps, stream);
+  }
   const int threads = E >= 1024 ? 256 : (E >= 256 ? 128 : 64);
   if (out_dtype == RB_F32)
     RB_LAUNCH("layernorm_kernel", (layernorm_kernel<float>), T, threads, 0, stream, (float*)out, x, w, b, E, eps);
@@ -746,40 +803,45 @@ __global__ void __launch_bounds__(256) norm_rotate_append_rows_kernel(
 }
 
 // The same rows with a norm per head AFTER the rotation: every q and k head is turned (a prefix of it) and then
-// divided by its own root mean square over its D values (no weight).  One warp per (token, head); a lane holds
-// every 32nd value of the head in registers (D up to 32 * HN_MAX).
+// divided by its own root mean square over its D values (no weight).  A block per token (its heads spread over several
+// blocks when tokens are few) makes the sines and cosines of the token's position once; then a warp per head, a lane
+// holding every 32nd value of the head in registers (D up to 32 * HN_MAX).
 constexpr int HN_MAX = 16;
-template <typename T>
-__global__ void __launch_bounds__(128) rotate_headnorm_append_kernel(
+template <typename T, int NG>      // NG: groups of 32 values a head's cache row holds at most
+__global__ void __launch_bounds__(256) rotate_headnorm_append_kernel(
     T* __restrict__ q_out, const T* __restrict__ proj, int64_t ld, float eps, const double* __restrict__ freq, float magnitude,
     const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, RbPagedLayer cache, int n_tokens, int H, int D, int Dv,
-    int rot_dim, int interleaved, int write_kv) {
+    int rot_dim, int interleaved, int write_kv, int heads_per_block) {
   rb_pdl_launch_dependents();
+  extern __shared__ float s_sincos[];              // rot_dim/2 sines, then as many cosines, of this token's position
   rb_pdl_wait();
   const int Dc = cache.head_dim, Kh = cache.n_kv_heads;
   const int per_token = H + (write_kv ? 2 * Kh : 0);
   const int lane = threadIdx.x & 31;
-  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (item >= (int64_t)n_tokens * per_token) return;
-  const int t = (int)(item / per_token), head = (int)(item % per_token);
+  const int t = blockIdx.x;
   const int pos = tok_pos[t], slot = tok_slot[t];
+  const int rhalf = rot_dim / 2;
+  for (int i = threadIdx.x; i < rhalf; i += blockDim.x)
+    rb_angle_sincos(pos, freq[i], magnitude, &s_sincos[i], &s_sincos[rhalf + i]);
+  __syncthreads();
   const T* row = proj + (int64_t)t * ld;
+  const int h_end = min(per_token, (int)(blockIdx.y + 1) * heads_per_block);
+  for (int head = blockIdx.y * heads_per_block + (threadIdx.x >> 5); head < h_end; head += blockDim.x >> 5) {
   if (head >= H + Kh) {
     // a value head: copied, padded with zeros
     const int kvh = head - H - Kh;
     T* dst = (T*)cache.v + rb_page_offset(cache, slot, pos, kvh);
     const T* src = row + (int64_t)(H + Kh) * D + kvh * Dv;
     for (int e = lane; e < Dc; e += 32) dst[e] = e < Dv ? src[e] : rb_from_float<T>(0.f);
-    return;
+    continue;
   }
   const bool is_q = head < H;
   T* dst = is_q ? q_out + ((int64_t)t * H + head) * Dc : (T*)cache.k + rb_page_offset(cache, slot, pos, head - H);
   const T* src = row + (int64_t)head * D;
-  const int rhalf = rot_dim / 2;
-  float y[HN_MAX];
+  float y[NG];
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < HN_MAX; ++i) {
+  for (int i = 0; i < NG; ++i) {
     const int e = lane + 32 * i;
     y[i] = 0.f;
     if (e >= D) continue;
@@ -791,8 +853,7 @@ __global__ void __launch_bounds__(128) rotate_headnorm_append_kernel(
       bool first;
       if (interleaved) { pair = e >> 1; first = (e & 1) == 0; other = first ? e + 1 : e - 1; }
       else { first = e < rhalf; pair = first ? e : e - rhalf; other = first ? e + rhalf : e - rhalf; }
-      float sn, cs;
-      rb_angle_sincos(pos, freq[pair], magnitude, &sn, &cs);
+      const float sn = s_sincos[pair], cs = s_sincos[rhalf + pair];
       const float ot = rb_to_float<T>(src[other]);
       y[i] = first ? me * cs - ot * sn : me * cs + ot * sn;
     }
@@ -801,9 +862,10 @@ __global__ void __launch_bounds__(128) rotate_headnorm_append_kernel(
   ss = rb_warp_sum(ss);
   const float r = 1.0f / sqrtf(ss / (float)D + eps);
 #pragma unroll
-  for (int i = 0; i < HN_MAX; ++i) {
+  for (int i = 0; i < NG; ++i) {
     const int e = lane + 32 * i;
     if (e < Dc) dst[e] = rb_from_float<T>(e < D ? y[i] * r : 0.f);
+  }
   }
 }
 
@@ -823,14 +885,34 @@ RB_EXPORT int rb_norm_rotate_append(void* q_out, const void* proj, int64_t ld, i
   RbPagedLayer c{cache_k, cache_v, page_table, max_pages, page_size, Kh, Dc};
   if (head_norm) {
     RB_REQUIRE(Dc <= 32 * HN_MAX, "rb_norm_rotate_append: a norm per head for heads of up to %d values (found %d)", 32 * HN_MAX, Dc);
-    const int64_t items = (int64_t)T * (H + (write_kv ? 2 * Kh : 0));
-    const int blocks = (int)((items + 3) / 4);
-    if (dtype == RB_F32)
-      RB_LAUNCH("rotate_headnorm_append_kernel", (rotate_headnorm_append_kernel<float>), blocks, 128, 0, stream, (float*)q_out, (const float*)proj, ld, eps, freq, magnitude, tok_pos, tok_slot, c, T, H, D, Dv, rot_dim, interleaved, write_kv);
-    else if (dtype == RB_BF16)
-      RB_LAUNCH("rotate_headnorm_append_kernel", (rotate_headnorm_append_kernel<__nv_bfloat16>), blocks, 128, 0, stream, (__nv_bfloat16*)q_out, (const __nv_bfloat16*)proj, ld, eps, freq, magnitude, tok_pos, tok_slot, c, T, H, D, Dv, rot_dim, interleaved, write_kv);
-    else
-      RB_FAIL("rb_norm_rotate_append: unknown dtype %d", dtype);
+    // few tokens: spread a token's heads over several blocks so that enough blocks run
+    const int per_token = H + (write_kv ? 2 * Kh : 0);
+    int by = T >= 128 ? 1 : (128 + T - 1) / T;
+    if (by > per_token) by = per_token;
+    const int hpb = (per_token + by - 1) / by;
+    const dim3 blocks(T, (per_token + hpb - 1) / hpb);
+    const int threads = hpb >= 4 ? 128 : (hpb >= 2 ? 64 : 32);
+    const size_t table = (size_t)rot_dim * sizeof(float);
+    const int groups = (Dc + 31) / 32;
+#define HN_GO(NG)                                                                                                                  \
+  do {                                                                                                                             \
+    if (dtype == RB_F32)                                                                                                           \
+      RB_LAUNCH("rotate_headnorm_append_kernel", (rotate_headnorm_append_kernel<float, NG>), blocks, threads, table, stream,       \
+                (float*)q_out, (const float*)proj, ld, eps, freq, magnitude, tok_pos, tok_slot, c, T, H, D, Dv, rot_dim,           \
+                interleaved, write_kv, hpb);                                                                                       \
+    else if (dtype == RB_BF16)                                                                                                     \
+      RB_LAUNCH("rotate_headnorm_append_kernel", (rotate_headnorm_append_kernel<__nv_bfloat16, NG>), blocks, threads, table,       \
+                stream, (__nv_bfloat16*)q_out, (const __nv_bfloat16*)proj, ld, eps, freq, magnitude, tok_pos, tok_slot, c, T, H,   \
+                D, Dv, rot_dim, interleaved, write_kv, hpb);                                                                       \
+    else                                                                                                                           \
+      RB_FAIL("rb_norm_rotate_append: unknown dtype %d", dtype);                                                                   \
+  } while (0)
+    if (groups <= 1) HN_GO(1);
+    else if (groups <= 2) HN_GO(2);
+    else if (groups <= 4) HN_GO(4);
+    else if (groups <= 8) HN_GO(8);
+    else HN_GO(16);
+#undef HN_GO
     RB_CHECK_LAUNCH("rb_norm_rotate_append");
     return 0;
   }
@@ -878,10 +960,58 @@ __global__ void head_gate_kernel(T* __restrict__ out, const T* __restrict__ a, c
   }
 }
 
+// The same for bfloat16 rows in groups of eight values (Dv and Dc multiples of 8, 16-byte aligned rows).
+__global__ void head_gate_rows_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ a,
+                                      const __nv_bfloat16* __restrict__ gate, int64_t ldg, int64_t n8, int H, int Dv, int Dc,
+                                      int per_value) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  const int per_row = H * Dv / 8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / per_row;
+    const int r = (int)(i - t * per_row) * 8;
+    const int h = r / Dv, j = r - h * Dv;
+    const uint4 raw = *reinterpret_cast<const uint4*>(a + (t * H + h) * Dc + j);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { const float2 f = __bfloat1622float2(p2[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+    if (gate != nullptr && per_value) {
+      const uint4 graw = *reinterpret_cast<const uint4*>(gate + t * ldg + r);
+      const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&graw);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(g2[k]);
+        v[2 * k] *= 1.0f / (1.0f + expf(-f.x));
+        v[2 * k + 1] *= 1.0f / (1.0f + expf(-f.y));
+      }
+    } else if (gate != nullptr) {
+      const float g = 1.0f / (1.0f + expf(-__bfloat162float(gate[t * ldg + h])));
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] *= g;
+    }
+    uint4 res;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o2[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+    *reinterpret_cast<uint4*>(out + t * (int64_t)H * Dv + r) = res;
+  }
+}
+
 RB_EXPORT int rb_head_gate(void* out, const void* a, const void* gate, int64_t ldg, int dtype, int T, int H, int Dv, int Dc,
                            int per_value, cudaStream_t stream) {
   if (T == 0) return 0;
   const int64_t n = (int64_t)T * H * Dv;
+  if (dtype == RB_BF16 && Dv % 8 == 0 && Dc % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)a % 16 == 0 &&
+      (gate == nullptr || !per_value || (ldg % 8 == 0 && (uintptr_t)gate % 16 == 0))) {
+    const int64_t n8 = n / 8;
+    const int64_t most8 = (int64_t)rb_sm_count() * 16;
+    const int blocks8 = (int)((n8 + 255) / 256 < most8 ? (n8 + 255) / 256 : most8);
+    RB_LAUNCH("head_gate_rows_kernel", (head_gate_rows_kernel), blocks8, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)a,
+              (const __nv_bfloat16*)gate, ldg, n8, H, Dv, Dc, per_value);
+    RB_CHECK_LAUNCH("rb_head_gate");
+    return 0;
+  }
   const int threads = 256;
   const int64_t most = (int64_t)rb_sm_count() * 16;
   const int blocks = (int)((n + threads - 1) / threads < most ? (n + threads - 1) / threads : most);

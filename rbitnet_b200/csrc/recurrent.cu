@@ -26,15 +26,18 @@ __device__ __forceinline__ float gelu_tanh_(float z) {
 // (with its bias) of position q of the slot's sequence is kept at row q mod K, so that writing a position
 // never touches one of the K-1 positions before it, which the same step may still be reading; zeros at
 // the start of a sequence.  tok_first: row of the first token of the row's run (null: every row is its own run).
+constexpr int CONV_TOKENS = 8;
 template <typename TI>
 __global__ void conv_causal_kernel(float* __restrict__ u, const TI* __restrict__ x, int64_t ldx, int x_off,
                                    const float* __restrict__ x_bias, const float* __restrict__ taps,
                                    const float* __restrict__ conv_bias, const float* __restrict__ tail,
                                    const int* __restrict__ tok_first, const int* __restrict__ tok_slot,
-                                   const int* __restrict__ tok_pos, int C, int K, int silu) {
+                                   const int* __restrict__ tok_pos, int n_tokens, int C, int K, int silu, int per_block) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
-  const int t = blockIdx.x;
+  // with many rows a block takes per_block neighbouring rows in turn: the earlier rows a row reads are then mostly in
+  // the SM's cache
+  for (int t = blockIdx.x * per_block; t < min(n_tokens, (int)(blockIdx.x + 1) * per_block); ++t) {
   const int first = tok_first != nullptr ? tok_first[t] : t;
   const int slot = tok_slot[t], pos = tok_pos[t];
   const int j = t - first;                      // rows of this run before this one
@@ -49,6 +52,7 @@ __global__ void conv_causal_kernel(float* __restrict__ u, const TI* __restrict__
       acc = fmaf(taps[(int64_t)c * K + (K - 1 - d)], v, acc);
     }
     u[(int64_t)t * C + c] = silu ? acc * sigmoidf_(acc) : acc;
+  }
   }
 }
 
@@ -528,11 +532,12 @@ RB_EXPORT int rb_conv_causal(float* u, const void* x, int64_t ldx, int x_off, in
   const int threads = 128;
   int by = (C + threads - 1) / threads;
   if (by > 64) by = 64;
-  const dim3 grid(T, by);
+  const int per_block = T >= 512 ? CONV_TOKENS : 1;
+  const dim3 grid((T + per_block - 1) / per_block, by);
   if (x_dtype == RB_F32)
-    RB_LAUNCH("conv_causal_kernel", (conv_causal_kernel<float>), grid, threads, 0, stream, u, (const float*)x, ldx, x_off, x_bias, taps, conv_bias, tail, tok_first, tok_slot, tok_pos, C, K, silu);
+    RB_LAUNCH("conv_causal_kernel", (conv_causal_kernel<float>), grid, threads, 0, stream, u, (const float*)x, ldx, x_off, x_bias, taps, conv_bias, tail, tok_first, tok_slot, tok_pos, T, C, K, silu, per_block);
   else if (x_dtype == RB_BF16)
-    RB_LAUNCH("conv_causal_kernel", (conv_causal_kernel<__nv_bfloat16>), grid, threads, 0, stream, u, (const __nv_bfloat16*)x, ldx, x_off, x_bias, taps, conv_bias, tail, tok_first, tok_slot, tok_pos, C, K, silu);
+    RB_LAUNCH("conv_causal_kernel", (conv_causal_kernel<__nv_bfloat16>), grid, threads, 0, stream, u, (const __nv_bfloat16*)x, ldx, x_off, x_bias, taps, conv_bias, tail, tok_first, tok_slot, tok_pos, T, C, K, silu, per_block);
   else
     RB_FAIL("rb_conv_causal: unknown dtype %d", x_dtype);
   RB_CHECK_LAUNCH("rb_conv_causal");

@@ -34,59 +34,11 @@ __device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
   v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
 }
 
-constexpr int ROUTE_TB = 8;
-
-template <typename TI>
-__global__ void __launch_bounds__(256) route_kernel(int* __restrict__ ids, float* __restrict__ weights,
-                                                    const TI* __restrict__ h, int64_t ldh,
-                                                    const float* __restrict__ Wr, const float* __restrict__ correction,
-                                                    int T, int K, int n, int top, int groups, int keep, int TB, int vec) {
-  rb_pdl_launch_dependents();
-  extern __shared__ float s_route[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int per_token = 2 * n + 2 * groups;
-  const int t0 = blockIdx.x * TB;
-  const int nt = min(TB, T - t0);
-  rb_pdl_wait();
-  for (int e = warp; e < n; e += 8) {
-    const float* w = Wr + (int64_t)e * K;
-    float acc[ROUTE_TB];
-#pragma unroll
-    for (int j = 0; j < ROUTE_TB; ++j) acc[j] = 0.f;
-    if (vec) {
-      for (int k = lane * 4; k < K; k += 128) {
-        float wv[4];
-        load4(w + k, wv);
-#pragma unroll
-        for (int j = 0; j < ROUTE_TB; ++j) {
-          if (j < nt) {
-            float hv[4];
-            load4(h + (int64_t)(t0 + j) * ldh + k, hv);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[j] = fmaf(hv[i], wv[i], acc[j]);
-          }
-        }
-      }
-    } else {
-      for (int k = lane; k < K; k += 32) {
-        const float wk = w[k];
-#pragma unroll
-        for (int j = 0; j < ROUTE_TB; ++j)
-          if (j < nt) acc[j] = fmaf(rb_to_float<TI>(h[(int64_t)(t0 + j) * ldh + k]), wk, acc[j]);
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < ROUTE_TB; ++j) {
-      const float v = rb_warp_sum(acc[j]);
-      if (lane == 0 && j < nt) s_route[(size_t)j * per_token + e] = v;
-    }
-  }
-  __syncthreads();
-  if (warp >= nt) return;
-  const int t = t0 + warp;
-  float* z = s_route + (size_t)warp * per_token;     // scores, choice scores, group scores, kept groups
-  float* choice = z + n;
-  float* gscore = choice + n;
+// One warp: from the token's router sums z[0..n) (shared memory; choice, gscore: n and 2 groups floats of scratch) to
+// its `top` outputs and their weights.
+__device__ __forceinline__ void route_select(float* z, float* choice, float* gscore, const float* __restrict__ correction,
+                                             int n, int top, int groups, int keep, int lane, int* __restrict__ ids,
+                                             float* __restrict__ weights, int64_t t) {
   float m = -INFINITY;
   for (int e = lane; e < n; e += 32) m = fmaxf(m, z[e]);
   m = rb_warp_max(m);
@@ -150,6 +102,159 @@ __global__ void __launch_bounds__(256) route_kernel(int* __restrict__ ids, float
   }
 }
 
+constexpr int ROUTE_TB = 8;
+
+template <typename TI>
+__global__ void __launch_bounds__(256) route_kernel(int* __restrict__ ids, float* __restrict__ weights,
+                                                    const TI* __restrict__ h, int64_t ldh,
+                                                    const float* __restrict__ Wr, const float* __restrict__ correction,
+                                                    int T, int K, int n, int top, int groups, int keep, int TB, int vec) {
+  rb_pdl_launch_dependents();
+  extern __shared__ float s_route[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per_token = 2 * n + 2 * groups;
+  const int t0 = blockIdx.x * TB;
+  const int nt = min(TB, T - t0);
+  rb_pdl_wait();
+  if (TB == 1 && vec) {
+    // one token: a warp makes four of its outputs at once, so that four rows of Wr are asked for together
+    const TI* row = h + (int64_t)t0 * ldh;
+    for (int e0 = warp; e0 < n; e0 += 32) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+      for (int k = lane * 4; k < K; k += 128) {
+        float hv[4];
+        load4(row + k, hv);
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          const int e = e0 + 8 * a;
+          if (e < n) {
+            float wv[4];
+            load4(Wr + (int64_t)e * K + k, wv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[a] = fmaf(hv[i], wv[i], acc[a]);
+          }
+        }
+      }
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        const float v = rb_warp_sum(acc[a]);
+        if (lane == 0 && e0 + 8 * a < n) s_route[e0 + 8 * a] = v;
+      }
+    }
+  } else
+  for (int e = warp; e < n; e += 8) {
+    const float* w = Wr + (int64_t)e * K;
+    float acc[ROUTE_TB];
+#pragma unroll
+    for (int j = 0; j < ROUTE_TB; ++j) acc[j] = 0.f;
+    if (vec) {
+#pragma unroll 4
+      for (int k = lane * 4; k < K; k += 128) {
+        float wv[4];
+        load4(w + k, wv);
+#pragma unroll
+        for (int j = 0; j < ROUTE_TB; ++j) {
+          if (j < nt) {
+            float hv[4];
+            load4(h + (int64_t)(t0 + j) * ldh + k, hv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[j] = fmaf(hv[i], wv[i], acc[j]);
+          }
+        }
+      }
+    } else {
+      for (int k = lane; k < K; k += 32) {
+        const float wk = w[k];
+#pragma unroll
+        for (int j = 0; j < ROUTE_TB; ++j)
+          if (j < nt) acc[j] = fmaf(rb_to_float<TI>(h[(int64_t)(t0 + j) * ldh + k]), wk, acc[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < ROUTE_TB; ++j) {
+      const float v = rb_warp_sum(acc[j]);
+      if (lane == 0 && j < nt) s_route[(size_t)j * per_token + e] = v;
+    }
+  }
+  __syncthreads();
+  if (warp >= nt) return;
+  float* z = s_route + (size_t)warp * per_token;     // scores, choice scores, group scores, kept groups
+  route_select(z, z + n, z + 2 * n, correction, n, top, groups, keep, lane, ids, weights, t0 + warp);
+}
+
+// Many tokens: the router's sums as a tiled float32 product (16 tokens by 64 outputs a block, k in steps of 32 through
+// shared memory, the next step's values asked for before this one is multiplied; every sum runs over k in ascending
+// order), then a warp per token for the choice.
+constexpr int RL_TM = 16, RL_TN = 64, RL_TK = 32;
+template <typename TI>
+__global__ void __launch_bounds__(256) route_logits_kernel(float* __restrict__ z, const TI* __restrict__ h, int64_t ldh,
+                                                           const float* __restrict__ Wr, int T, int K, int n) {
+  rb_pdl_launch_dependents();
+  __shared__ float As[RL_TK][RL_TM + 1];
+  __shared__ __align__(16) float Ws[RL_TK][RL_TN + 4];
+  const int tid = threadIdx.x, tok = tid >> 4, oo = (tid & 15) * 4;
+  const int t0 = blockIdx.x * RL_TM;
+  rb_pdl_wait();
+  // what a thread brings per step: two values of the tokens' rows, eight of the router's
+  const int a_row = tid >> 4, a_k = (tid & 15) * 2;           // token, k
+  const int w_row = tid >> 2, w_k = (tid & 3) * 8;            // output, k
+  for (int n0 = 0; n0 < n; n0 += RL_TN) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float a_next[2], w_next[8];
+    auto fetch = [&](int k0) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int k = k0 + a_k + i;
+        a_next[i] = (t0 + a_row < T && k < K) ? rb_to_float<TI>(h[(int64_t)(t0 + a_row) * ldh + k]) : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int k = k0 + w_k + i;
+        w_next[i] = (n0 + w_row < n && k < K) ? Wr[(int64_t)(n0 + w_row) * K + k] : 0.f;
+      }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < K; k0 += RL_TK) {
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < 2; ++i) As[a_k + i][a_row] = a_next[i];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) Ws[w_k + i][w_row] = w_next[i];
+      __syncthreads();
+      if (k0 + RL_TK < K) fetch(k0 + RL_TK);
+#pragma unroll
+      for (int kk = 0; kk < RL_TK; ++kk) {
+        const float a = As[kk][tok];
+        const float4 w = *reinterpret_cast<const float4*>(&Ws[kk][oo]);
+        acc[0] = fmaf(a, w.x, acc[0]); acc[1] = fmaf(a, w.y, acc[1]);
+        acc[2] = fmaf(a, w.z, acc[2]); acc[3] = fmaf(a, w.w, acc[3]);
+      }
+    }
+    if (t0 + tok < T) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (n0 + oo + i < n) z[(int64_t)(t0 + tok) * n + n0 + oo + i] = acc[i];
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(128) route_select_kernel(int* __restrict__ ids, float* __restrict__ weights,
+                                                           const float* __restrict__ zg, const float* __restrict__ correction,
+                                                           int T, int n, int top, int groups, int keep) {
+  rb_pdl_launch_dependents();
+  extern __shared__ float s_route[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  float* z = s_route + (size_t)warp * (2 * n + 2 * groups);
+  rb_pdl_wait();
+  if (t >= T) return;
+  for (int e = lane; e < n; e += 32) z[e] = zg[(int64_t)t * n + e];
+  __syncwarp();
+  route_select(z, z + n, z + 2 * n, correction, n, top, groups, keep, lane, ids, weights, t);
+}
+
 // ---------------------------------------------------------------- plan
 // One block.  ids: [pairs] chosen outputs.  Outputs:
 //   pos [pairs]        the pair's row in the padded buffer (-1: an identity expert)
@@ -205,6 +310,18 @@ __global__ void gather_kernel(T* __restrict__ xp, const T* __restrict__ h, int64
   const int r = blockIdx.x;
   const int t = row_token[r];
   T* dst = xp + (int64_t)r * K;
+  constexpr int PER = 16 / (int)sizeof(T);          // values in 16 bytes
+  const bool vec = K % PER == 0 && ldh % PER == 0 && (uintptr_t)xp % 16 == 0 && (uintptr_t)h % 16 == 0;
+  if (vec) {
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    if (t < 0) {
+      for (int k = threadIdx.x; k < K / PER; k += blockDim.x) d4[k] = make_uint4(0, 0, 0, 0);
+      return;
+    }
+    const uint4* s4 = reinterpret_cast<const uint4*>(h + (int64_t)t * ldh);
+    for (int k = threadIdx.x; k < K / PER; k += blockDim.x) d4[k] = s4[k];
+    return;
+  }
   if (t < 0) {
     for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = rb_from_float<T>(0.f);
     return;
@@ -218,10 +335,33 @@ __global__ void gather_kernel(T* __restrict__ xp, const T* __restrict__ h, int64
 template <typename T>
 __global__ void combine_kernel(float* __restrict__ x, int64_t ldx, const float* __restrict__ y, const T* __restrict__ h,
                                int64_t ldh, const int* __restrict__ pos, const float* __restrict__ weights, int top, int E,
-                               int accumulate) {
+                               int accumulate, int vec4) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
   const int t = blockIdx.x;
+  if (vec4) {
+    // four columns a thread: 16-byte loads of the experts' rows and of the residual stream
+    for (int c = threadIdx.x * 4; c < E; c += blockDim.x * 4) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int j = 0; j < top; ++j) {
+        const int r = pos[(int64_t)t * top + j];
+        const float w = weights[(int64_t)t * top + j];
+        float v[4];
+        if (r >= 0) load4(y + (int64_t)r * E + c, v);
+        else load4(h + (int64_t)t * ldh + c, v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] = fmaf(w, v[i], acc[i]);
+      }
+      float4* dst = reinterpret_cast<float4*>(x + (int64_t)t * ldx + c);
+      float4 out = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      if (accumulate) {
+        const float4 old = *dst;
+        out = make_float4(old.x + acc[0], old.y + acc[1], old.z + acc[2], old.w + acc[3]);
+      }
+      *dst = out;
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < E; c += blockDim.x) {
     float acc = 0.f;
     for (int j = 0; j < top; ++j) {
@@ -311,14 +451,32 @@ __global__ void square_relu_kernel(T* __restrict__ out, const T* __restrict__ in
 }  // namespace
 
 // ids, weights: [T, top].  h: the input rows (dtype h_dtype).  Wr: float32 [n, K]; correction: float32 [n] or null.
-// groups <= 1 or keep >= groups: every output can be chosen.
+// groups <= 1 or keep >= groups: every output can be chosen.  z_scratch: T * n floats (from 64 tokens on, the router's
+// sums are a product of their own that leaves them there), or null.
 RB_EXPORT int rb_route(int* ids, float* weights, const void* h, int64_t ldh, int h_dtype, const float* Wr,
-                       const float* correction, int T, int K, int n, int top, int groups, int keep, cudaStream_t stream) {
+                       const float* correction, int T, int K, int n, int top, int groups, int keep, float* z_scratch,
+                       cudaStream_t stream) {
   if (T == 0) return 0;
   RB_REQUIRE(K > 0 && n > 0 && top > 0 && top <= n, "rb_route: bad sizes K=%d outputs=%d top=%d", K, n, top);
   RB_REQUIRE(groups <= 1 || n % groups == 0, "rb_route: %d outputs are not %d equal groups", n, groups);
   if (groups < 1) groups = 1;
   // few tokens: a block each, so that the rows of Wr are read by many SMs at once; many: eight tokens a block
+  if (T >= 64 && z_scratch != nullptr) {
+    const size_t smem_sel = (size_t)4 * (2 * n + 2 * groups) * sizeof(float);
+    RB_REQUIRE(smem_sel <= 48 * 1024, "rb_route: %d router outputs are more than a block's shared memory holds", n);
+    const int blocks_l = (T + RL_TM - 1) / RL_TM;
+    if (h_dtype == RB_F32)
+      RB_LAUNCH("route_logits_kernel", (route_logits_kernel<float>), blocks_l, 256, 0, stream, z_scratch, (const float*)h, ldh, Wr, T, K, n);
+    else if (h_dtype == RB_BF16)
+      RB_LAUNCH("route_logits_kernel", (route_logits_kernel<__nv_bfloat16>), blocks_l, 256, 0, stream, z_scratch, (const __nv_bfloat16*)h, ldh, Wr, T, K, n);
+    else
+      RB_FAIL("rb_route: unknown dtype %d", h_dtype);
+    RB_CHECK_LAUNCH("rb_route");
+    RB_LAUNCH("route_select_kernel", (route_select_kernel), (T + 3) / 4, 128, smem_sel, stream, ids, weights, z_scratch, correction, T, n, top,
+              groups, keep);
+    RB_CHECK_LAUNCH("rb_route");
+    return 0;
+  }
   const int TB = T >= 64 ? ROUTE_TB : 1;
   const size_t smem = (size_t)TB * (2 * n + 2 * groups) * sizeof(float);
   RB_REQUIRE(smem <= 48 * 1024, "rb_route: %d router outputs are more than a block's shared memory holds", n);
@@ -332,6 +490,21 @@ RB_EXPORT int rb_route(int* ids, float* weights, const void* h, int64_t ldh, int
   else
     RB_FAIL("rb_route: unknown dtype %d", h_dtype);
   RB_CHECK_LAUNCH("rb_route");
+  return 0;
+}
+
+// The choice alone, from router sums z [T, n] that a product has left (float32).
+RB_EXPORT int rb_route_select(int* ids, float* weights, const float* z, const float* correction, int T, int n, int top,
+                              int groups, int keep, cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(n > 0 && top > 0 && top <= n, "rb_route_select: bad sizes outputs=%d top=%d", n, top);
+  RB_REQUIRE(groups <= 1 || n % groups == 0, "rb_route_select: %d outputs are not %d equal groups", n, groups);
+  if (groups < 1) groups = 1;
+  const size_t smem_sel = (size_t)4 * (2 * n + 2 * groups) * sizeof(float);
+  RB_REQUIRE(smem_sel <= 48 * 1024, "rb_route_select: %d router outputs are more than a block's shared memory holds", n);
+  RB_LAUNCH("route_select_kernel", (route_select_kernel), (T + 3) / 4, 128, smem_sel, stream, ids, weights, z, correction, T, n, top,
+            groups, keep);
+  RB_CHECK_LAUNCH("rb_route_select");
   return 0;
 }
 
@@ -372,11 +545,14 @@ RB_EXPORT int rb_routed_combine(float* x, int64_t ldx, const float* y, const voi
                                 const int* pos, const float* weights, int T, int top, int E, int accumulate,
                                 cudaStream_t stream) {
   if (T == 0) return 0;
-  const int threads = E >= 256 ? 256 : (E >= 128 ? 128 : 64);
+  const int elem = h_dtype == RB_F32 ? 4 : 2;
+  const int vec4 = E % 4 == 0 && ldx % 4 == 0 && ldh % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0 &&
+                   (uintptr_t)h % (4 * elem) == 0;
+  const int threads = vec4 ? (E >= 1024 ? 256 : (E >= 512 ? 128 : 64)) : (E >= 256 ? 256 : (E >= 128 ? 128 : 64));
   if (h_dtype == RB_F32)
-    RB_LAUNCH("combine_kernel", (combine_kernel<float>), T, threads, 0, stream, x, ldx, y, (const float*)h, ldh, pos, weights, top, E, accumulate);
+    RB_LAUNCH("combine_kernel", (combine_kernel<float>), T, threads, 0, stream, x, ldx, y, (const float*)h, ldh, pos, weights, top, E, accumulate, vec4);
   else if (h_dtype == RB_BF16)
-    RB_LAUNCH("combine_kernel", (combine_kernel<__nv_bfloat16>), T, threads, 0, stream, x, ldx, y, (const __nv_bfloat16*)h, ldh, pos, weights, top, E, accumulate);
+    RB_LAUNCH("combine_kernel", (combine_kernel<__nv_bfloat16>), T, threads, 0, stream, x, ldx, y, (const __nv_bfloat16*)h, ldh, pos, weights, top, E, accumulate, vec4);
   else
     RB_FAIL("rb_routed_combine: unknown dtype %d", h_dtype);
   RB_CHECK_LAUNCH("rb_routed_combine");

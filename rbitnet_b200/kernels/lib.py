@@ -32,11 +32,14 @@ _SIGNATURES = {
     "rb_gated_act": [P, P, I, I, I, I, L, I, F, F, F, P],
     "rb_conv_causal": [P, P, L, I, I, P, P, P, P, P, P, P, I, I, I, I, P],
     "rb_conv_tail_update": [P, P, L, I, I, P, P, P, P, P, I, I, I, P],
-    "rb_delta_prepare": [P, L, P, L, I, I, P, P, P, P, P, I, I, I, I, F, F, P],
+    "rb_delta_prepare": [P, L, P, L, I, I, P, P, P, P, P, P, I, I, I, I, F, F, P],
+    "rb_gated_delta_chunked": [P, P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+    "rb_gated_delta_chunked_supports": [I, I, ctypes.c_longlong, I],
     "rb_gated_delta": [P, P, L, P, P, P, P, P, P, P, I, I, I, I, I, P],
     "rb_layernorm": [P, I, P, P, P, I, I, F, P],
     "rb_add_rows": [P, P, ctypes.c_longlong, P],
-    "rb_route": [P, P, P, L, I, P, P, I, I, I, I, I, I, P],
+    "rb_route": [P, P, P, L, I, P, P, I, I, I, I, I, I, P, P],
+    "rb_route_select": [P, P, P, P, I, I, I, I, I, P],
     "rb_routed_tiles": [I, I, I],
     "rb_routed_plan": [P, P, P, P, I, I, I, I, I, P],
     "rb_routed_gather": [P, P, L, I, P, I, I, P],
@@ -96,6 +99,7 @@ class KernelLibrary:
         self.declare("rb_attention_decode_parts", [I, I, I])
         self.declare("rb_gemm_tc_splits", [I, I, I])
         self.declare("rb_gemm_tc_workspace_bytes", [], restype=ctypes.c_longlong)
+        self.declare("rb_gated_delta_chunk_floats", [I, I], restype=ctypes.c_longlong)
         self.declare("rb_gemm_tc_set_workspace", [P, L])
         self.declare("rb_gemm_tc_plan", [I, I, I, I, I, I, P])
         self.declare("rb_gemm_tc_share_for_test", [I])

@@ -124,6 +124,8 @@ class CudaOps:
         self.fuse_gated_act = True
         #: a decode step's gated linear recurrence (convolution, gates, scan) is one kernel for up to 16 rows
         self.fuse_recurrent_step = True
+        #: the delta rule takes runs of several tokens in chunks of 32 (else token by token, as a decode step does)
+        self.delta_in_chunks = True
         #: tensor-core products of more than 256 tokens may share a weight tile's inner dimension
         #: between teams of CTAs (needs the workspace; tiles are taken in turn without it)
         _give_gemm_workspace(self.lib, self.device)
@@ -654,6 +656,23 @@ class CudaOps:
                       at["g"], T, H, Dv, float(p.norm_eps), 0, 0, self._stream())
         return out
 
+    def _delta_chunks(self, meta, size: int = 32):
+        """The step's runs cut into chunks of ``size`` rows (device int32: per run its first chunk; per chunk its first
+        row and its rows), made once per step."""
+        key = ("delta_chunks", size)
+        if key not in meta.extra:
+            import numpy as np
+            run0, rows, lens = [], [], []
+            for c in meta.seqs:
+                run0.append(len(rows))
+                for a in range(0, c.n_new, size):
+                    rows.append(c.offset + a)
+                    lens.append(min(size, c.n_new - a))
+            dev = torch.from_numpy(np.asarray(run0 + rows + lens, dtype=np.int32)).to(self.device)
+            n, k = len(run0), len(rows)
+            meta.extra[key] = (dev[:n], dev[n:n + k], dev[n + k:], k)
+        return meta.extra[key]
+
     def gated_delta(self, proj: torch.Tensor, p, state, meta) -> torch.Tensor:
         """The gated delta rule of ``parts.delta.GatedDeltaRule`` ``p`` on float32 rows [q | k | v | g | b | a] of its
         stacked projection: short convolution and SiLU of q, k, v; unit vectors; gates; the recurrence; the heads'
@@ -668,14 +687,23 @@ class CudaOps:
         u = torch.empty((T, C), dtype=torch.float32, device=self.device)
         self.lib.call("rb_conv_causal", _ptr(u), _ptr(proj), proj.stride(0), 0, F32, c_void_p(0), _ptr(p.conv_w), c_void_p(0),
                       _ptr(tail), _ptr(tok_first), _ptr(meta.tok_slot), _ptr(meta.tok_pos), T, C, K, 1, self._stream())
-        gates = torch.empty((T * (2 * H + G),), dtype=torch.float32, device=self.device)
-        beta, decay, kq = gates[:T * H], gates[T * H:2 * T * H], gates[2 * T * H:]
+        gates = torch.empty((T * (3 * H + G),), dtype=torch.float32, device=self.device)
+        beta, decay, log_decay, kq = gates[:T * H], gates[T * H:2 * T * H], gates[2 * T * H:3 * T * H], gates[3 * T * H:]
         self.lib.call("rb_delta_prepare", _ptr(u), u.stride(0), _ptr(proj), proj.stride(0), at["b"], at["a"], _ptr(p.a_log),
-                      _ptr(p.dt_bias), _ptr(beta), _ptr(decay), _ptr(kq), T, H, G, D, float(D) ** -0.5, float(p.unit_eps),
-                      self._stream())
+                      _ptr(p.dt_bias), _ptr(beta), _ptr(decay), _ptr(log_decay), _ptr(kq), T, H, G, D, float(D) ** -0.5,
+                      float(p.unit_eps), self._stream())
         o = torch.empty((T, H * Dv), dtype=torch.float32, device=self.device)
-        self.lib.call("rb_gated_delta", _ptr(o), _ptr(u), u.stride(0), _ptr(beta), _ptr(decay), _ptr(kq), _ptr(state["S"]),
-                      _ptr(first), _ptr(count), _ptr(meta.tok_slot), n_runs, H, G, D, Dv, self._stream())
+        if first is not None and self.delta_in_chunks and self.lib.raw("rb_gated_delta_chunked_supports")(D, Dv, u.stride(0), G):
+            # runs of several tokens: chunks of 32, the chain in time only from chunk to chunk
+            run_chunk0, chunk_row, chunk_len, n_chunks = self._delta_chunks(meta)
+            scratch = torch.empty((n_chunks * H * self.lib.raw("rb_gated_delta_chunk_floats")(D, Dv),), dtype=torch.float32,
+                                  device=self.device)
+            self.lib.call("rb_gated_delta_chunked", _ptr(o), _ptr(u), u.stride(0), _ptr(beta), _ptr(log_decay), _ptr(state["S"]),
+                          _ptr(scratch), _ptr(first), _ptr(count), _ptr(run_chunk0), _ptr(chunk_row), _ptr(chunk_len),
+                          _ptr(meta.tok_slot), n_runs, n_chunks, H, G, D, Dv, self._stream(), launches=2)
+        else:
+            self.lib.call("rb_gated_delta", _ptr(o), _ptr(u), u.stride(0), _ptr(beta), _ptr(decay), _ptr(kq), _ptr(state["S"]),
+                          _ptr(first), _ptr(count), _ptr(meta.tok_slot), n_runs, H, G, D, Dv, self._stream())
         if K > 1:
             self.lib.call("rb_conv_tail_update", _ptr(tail), _ptr(proj), proj.stride(0), 0, F32, c_void_p(0), _ptr(first),
                           _ptr(count), _ptr(meta.tok_slot), _ptr(meta.tok_pos), n_runs, C, K, self._stream())
@@ -685,18 +713,37 @@ class CudaOps:
         return out
 
     # ------------------------------------------------------------------ routed experts
+    def prepare_router(self, router: torch.Tensor) -> Optional[LinearWeight]:
+        """The router's matrix for the tensor-core product, if that product gives the float32 sums: in bfloat16 mode, for
+        a matrix whose float32 values are bfloat16 values (then every product of an input value and a weight is exact in
+        float32 and the sums are float32 sums); else None, and the router's sums are FFMA sums on the float32 matrix."""
+        if self.dtype != torch.bfloat16:
+            return None
+        w = router.to(device=self.device, dtype=torch.float32)
+        if not bool(torch.equal(w.to(torch.bfloat16).to(torch.float32), w)):
+            return None
+        return self.prepare_linear([w])
+
     def route(self, h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int,
-              keep: int):
+              keep: int, router_tc: Optional[LinearWeight] = None):
         """(ids int32 [T, top], weights float32 [T, top]): softmax of the float32 router product over all outputs; the
         ``top`` largest scores plus ``correction`` among the outputs of the ``keep`` best of ``groups`` equal groups;
-        the weights are the scores themselves."""
+        the weights are the scores themselves.  ``router_tc``: what ``prepare_router`` gave (many tokens then take the
+        tensor-core product for the sums)."""
         self._check(h, self.dtype, "route input")
         T, K = h.shape
         n = router.shape[0]
         ids = torch.empty((T, top), dtype=torch.int32, device=self.device)
         weights = torch.empty((T, top), dtype=torch.float32, device=self.device)
+        if T >= 64 and router_tc is not None and self._tensor_core_ok(h, router_tc.w):
+            z = self.linear(h, router_tc, out_dtype=torch.float32)
+            self.lib.call("rb_route_select", _ptr(ids), _ptr(weights), _ptr(z), _ptr(correction), T, n, int(top), int(groups),
+                          int(keep), self._stream())
+            return ids, weights
+        # from 64 tokens on the router's sums are a tiled product of their own, which leaves them in z
+        z = torch.empty((T, n), dtype=torch.float32, device=self.device) if T >= 64 else None
         self.lib.call("rb_route", _ptr(ids), _ptr(weights), _ptr(h), h.stride(0), self.code, _ptr(router), _ptr(correction),
-                      T, K, n, int(top), int(groups), int(keep), self._stream())
+                      T, K, n, int(top), int(groups), int(keep), _ptr(z), self._stream(), launches=2 if z is not None else 1)
         return ids, weights
 
     def routed_tile(self, pairs: int, n_experts: int, inner: int, width: int) -> int:

@@ -102,7 +102,7 @@ class RoutedExperts(FeedForward):
                 raise ValueError(f"routed experts: {n} router outputs are not {self.groups} equal groups")
             if not 1 <= self.keep <= self.groups:
                 raise ValueError(f"routed experts: {self.keep} of {self.groups} groups kept")
-        self.router = self.correction = self.w_up = self.w_down = None
+        self.router = self.router_tc = self.correction = self.w_up = self.w_down = None
 
     def weight_shapes(self):
         n = self.n_experts + self.n_identity
@@ -119,6 +119,9 @@ class RoutedExperts(FeedForward):
         self.router = weights["router"].to(device=ops.device, dtype=torch.float32).contiguous()
         self.correction = (weights["correction"].to(device=ops.device, dtype=torch.float32).contiguous()
                            if self.has_correction else None)
+        # where the operations can make the same float32 sums on the tensor cores, they say so here
+        prepare = getattr(ops, "prepare_router", None)
+        self.router_tc = prepare(weights["router"]) if prepare is not None else None
         if self.n_experts:
             # the experts' matrices one below the other: [n_experts * inner, width] and [n_experts * width, inner]
             self.w_up = ops.prepare_linear([weights[f"e{e}.up"] for e in range(self.n_experts)])
@@ -126,7 +129,10 @@ class RoutedExperts(FeedForward):
 
     def forward(self, ctx, h, accumulate_into=None):
         ops = ctx.ops
-        ids, weights = ops.route(h, self.router, self.correction, self.top, self.groups, self.keep)
+        if self.router_tc is not None:
+            ids, weights = ops.route(h, self.router, self.correction, self.top, self.groups, self.keep, router_tc=self.router_tc)
+        else:
+            ids, weights = ops.route(h, self.router, self.correction, self.top, self.groups, self.keep)
         return ops.routed_experts(h, ids, weights, self.w_up, self.w_down, self.n_experts, self.inner,
                                   accumulate_into=accumulate_into)
 

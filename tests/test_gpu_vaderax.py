@@ -141,12 +141,14 @@ def test_layer_norm_kernel(T, E):
 
 @pytest.mark.parametrize("n_experts,identity,top,groups", [(16, 4, 4, (4, 3)), (5, 0, 1, None), (3, 3, 3, (3, 3)), (60, 4, 6, (8, 3)),
                                                            (7, 2, 2, (3, 1)), (2, 0, 2, None), (130, 30, 8, (40, 5))])
-def test_router_kernel(n_experts, identity, top, groups):
+@pytest.mark.parametrize("T,K", [(50, 48), (333, 100), (7, 70)])
+def test_router_kernel(n_experts, identity, top, groups, T, K):
     """Scores, the choice among the kept groups by score plus correction, weights without it; corrections large
-    enough to change the choice, and negative choice scores in whole groups."""
+    enough to change the choice, and negative choice scores in whole groups.  Few tokens (a block per token) and many
+    (the router's sums as a tiled product), inner sizes that are and are not multiples of 4."""
     ops = _ops(torch.float32)
     g = torch.Generator().manual_seed(n_experts * 10 + top)
-    T, K, n = 50, 48, n_experts + identity
+    n = n_experts + identity
     h = torch.randn(T, K, generator=g).double()
     w = {"router": torch.randn(n, K, generator=g).double() * 0.3, "correction": torch.randn(n, generator=g).double() * 0.2 - 0.3}
     r = {"experts": n_experts, "identity": identity, "top": top}
@@ -159,10 +161,10 @@ def test_router_kernel(n_experts, identity, top, groups):
     for t in range(T):
         assert sorted(ids[t].tolist()) == sorted(want_ids[t].tolist()), t
         order = torch.argsort(ids[t]), torch.argsort(want_ids[t])
-        assert float((weights[t][order[0]] - want_w[t][order[1]]).abs().max()) <= 1e-6
+        assert float((weights[t][order[0]] - want_w[t][order[1]]).abs().max()) <= 3e-6
     # the correction decides: without it other experts are chosen somewhere
     other, _ = plain.route(h, r, {"router": w["router"], "correction": torch.zeros(n, dtype=torch.float64)})
-    assert any(sorted(other[t].tolist()) != sorted(want_ids[t].tolist()) for t in range(T)) or top == n
+    assert any(sorted(other[t].tolist()) != sorted(want_ids[t].tolist()) for t in range(T)) or top == n or T < 50
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -217,15 +219,18 @@ def test_dense_feed_forward(dtype, T):
     assert rel_err(part.forward(ctx, h.to(dtype).cuda()).cpu(), plain.dense_ff(h, w)) <= (1e-5 if dtype == torch.float32 else 2e-2)
 
 
+@pytest.mark.parametrize("chunks", [True, False])
 @pytest.mark.parametrize("H,G,D,Dv,K", [(4, 2, 16, 24, 3), (1, 1, 40, 8, 1), (6, 3, 32, 64, 4), (2, 2, 128, 64, 2), (3, 1, 100, 33, 5),
-                                        (2, 1, 8, 130, 2), (1, 1, 300, 20, 3), (2, 2, 600, 8, 2)])
-def test_gated_delta_kernels(H, G, D, Dv, K):
+                                        (2, 1, 8, 130, 2), (1, 1, 300, 20, 3), (2, 2, 600, 8, 2), (2, 1, 30, 16, 2)])
+def test_gated_delta_kernels(H, G, D, Dv, K, chunks):
     """Whole runs, portions and single tokens through the state and the convolution's ring; key sizes that one to
-    thirty-two lanes hold; decays near one, so that the memory of the first tokens is still there at the end."""
+    thirty-two lanes hold; decays near one, so that the memory of the first tokens is still there at the end.  Runs of
+    several tokens in chunks of 32 (a run of 100 tokens ends inside its fourth chunk) and token by token."""
     from rbitnet_b200.parts.delta import GatedDeltaRule
     ops = _ops(torch.float32)
+    ops.delta_in_chunks = chunks
     g = torch.Generator().manual_seed(H * 1000 + D)
-    E, T = 32, 45
+    E, T = 32, 100
     part = GatedDeltaRule(E, H, G, D, Dv, K, norm_eps=1e-5)
     w = {k: torch.randn(*shape, generator=g, dtype=torch.float64) * (0.3 if len(shape) > 1 and not k.endswith("conv") else 1.0)
          for k, (shape, _) in part.weight_shapes().items()}
@@ -238,7 +243,7 @@ def test_gated_delta_kernels(H, G, D, Dv, K):
     class Ctx:
         def state_view(self, entry):
             return state
-    for cuts in ([0, T], [0, 1, 2, 20, 36, 37, T], list(range(T + 1)), [0, 17, 33, T]):
+    for cuts in ([0, T], [0, 1, 2, 20, 36, 37, T], list(range(T + 1)), [0, 32, 33, 97, T], [0, 64, T]):
         state = {k: torch.zeros((3, *n.shape), device="cuda") for k, n in part.state_need().items()}
         outs = []
         for a, b in zip(cuts[:-1], cuts[1:]):
