@@ -212,6 +212,99 @@ int launch_delta(dim3 grid, size_t smem, cudaStream_t stream, float* o, const fl
   return 0;
 }
 
+// ---------------------------------------------------------------- a decode step in one launch
+// One token per sequence: a block per (row, head) does everything between the stacked product and the output product:
+// the convolution of the head's q, k and v channels from the ring of last inputs (and the ring's new row), SiLU, the
+// unit vectors, beta and the decay, one step of the memory for all of the head's value columns (a column on P lanes of
+// R rows each), the norm over the head's outputs, the weight and the SiLU gate.  q and k of a key head are made again by
+// every value head that reads it; the first of them writes their ring rows.
+template <int R>
+__global__ void __launch_bounds__(1024) delta_step_kernel(
+    void* __restrict__ out, int out_bf16, const float* __restrict__ proj, int64_t ld, int g_off, int b_off, int a_off,
+    const float* __restrict__ taps, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+    const float* __restrict__ norm_w, float* __restrict__ state, float* __restrict__ tail, const int* __restrict__ tok_slot,
+    const int* __restrict__ tok_pos, int H, int G, int D, int Dv, int K, int P, float q_scale, float unit_eps, float norm_eps) {
+  rb_pdl_launch_dependents();
+  extern __shared__ __align__(16) float s_step[];
+  __shared__ float scratch[33];
+  float* qs = s_step;            // [D]
+  float* ks = qs + D;            // [D]
+  float* vs = ks + D;            // [Dv]
+  const int t = blockIdx.x, h = blockIdx.y, kvh = h / (H / G), tid = threadIdx.x;
+  const int C = 2 * G * D + H * Dv;
+  rb_pdl_wait();
+  const int slot = tok_slot[t], pos = tok_pos[t];
+  const float* row = proj + (int64_t)t * ld;
+  const bool writes_qk = h % (H / G) == 0;
+  for (int i = tid; i < 2 * D + Dv; i += blockDim.x) {
+    const int ch = i < D ? kvh * D + i : (i < 2 * D ? (G + kvh) * D + (i - D) : 2 * G * D + h * Dv + (i - 2 * D));
+    const float x0 = row[ch];
+    float acc = taps[(int64_t)ch * K + (K - 1)] * x0;
+    for (int d = 1; d < K; ++d) {
+      if (pos - d < 0) break;
+      acc = fmaf(taps[(int64_t)ch * K + (K - 1 - d)], tail[((int64_t)slot * K + (pos - d) % K) * C + ch], acc);
+    }
+    if (K > 1 && (i >= 2 * D || writes_qk)) tail[((int64_t)slot * K + pos % K) * C + ch] = x0;
+    s_step[i] = acc * sigmoid_(acc);
+  }
+  __syncthreads();
+  float sq = 0.f, sk = 0.f;
+  for (int d = tid; d < D; d += blockDim.x) { sq = fmaf(qs[d], qs[d], sq); sk = fmaf(ks[d], ks[d], sk); }
+  sq = rb_block_sum(sq, scratch);
+  sk = rb_block_sum(sk, scratch);
+  const float rq = q_scale / sqrtf(sq + unit_eps), rk = 1.0f / sqrtf(sk + unit_eps);
+  float dot = 0.f;
+  for (int d = tid; d < D; d += blockDim.x) {
+    const float a = qs[d] * rq, b = ks[d] * rk;
+    qs[d] = a;
+    ks[d] = b;
+    dot = fmaf(a, b, dot);
+  }
+  dot = rb_block_sum(dot, scratch);          // (its barriers also make the finished q and k visible)
+  const float beta = sigmoid_(row[b_off + h]);
+  const float g = expf(-expf(A_log[h]) * softplus_(row[a_off + h] + dt_bias[h]));
+  const int p = tid % P, col = tid / P;
+  const bool live = col < Dv;
+  float o = 0.f;
+  {
+    // every thread walks this part, also those beyond the head's columns (with zeros): the lanes of a warp meet in the
+    // shuffles below
+    float* mine = state + (((int64_t)slot * H + h) * Dv + (live ? col : 0)) * D;
+    float S[R];
+    float rsum = 0.f, psum = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int d = p * R + r;
+      const bool in = live && d < D;
+      S[r] = in ? mine[d] : 0.f;
+      rsum = fmaf(S[r], in ? ks[d] : 0.f, rsum);
+      psum = fmaf(S[r], in ? qs[d] : 0.f, psum);
+    }
+    for (int off = P >> 1; off > 0; off >>= 1) {
+      rsum += __shfl_xor_sync(0xffffffffu, rsum, off);
+      psum += __shfl_xor_sync(0xffffffffu, psum, off);
+    }
+    if (live) {
+      const float w = beta * (vs[col] - g * rsum);
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int d = p * R + r;
+        if (d < D) mine[d] = fmaf(ks[d], w, g * S[r]);
+      }
+      o = fmaf(w, dot, g * psum);
+    }
+  }
+  const float ss = rb_block_sum(live && p == 0 ? o * o : 0.f, scratch);
+  if (live && p == 0) {
+    const float r = 1.0f / sqrtf(ss / (float)Dv + norm_eps);
+    const float gate = row[g_off + h * Dv + col];
+    const float y = o * r * norm_w[col] * (gate * sigmoid_(gate));
+    const int64_t at = ((int64_t)t * H + h) * Dv + col;
+    if (out_bf16) ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(y);
+    else ((float*)out)[at] = y;
+  }
+}
+
 // ---------------------------------------------------------------- long runs: chunks of 32 tokens
 // Within a chunk that starts from the memory S0, with L_i the sum of the logarithms of the decays of the chunk's tokens
 // up to i (so that exp(L_i - L_j) is the decay from token j to token i):
@@ -539,5 +632,41 @@ RB_EXPORT int rb_gated_delta_chunked(float* o, const float* u, int64_t ldu, cons
   RB_LAUNCH("delta_chunk_scan_kernel", (delta_chunk_scan_kernel), grid, 128, smem_b, stream, o, Wg, Utg, Mg, Lg, u, ldu, state,
             seq_first, seq_count, run_chunk0, tok_slot, H, G, D, Dv);
   RB_CHECK_LAUNCH("rb_gated_delta_chunked");
+  return 0;
+}
+
+// Lanes per value column of the one-launch decode step for these sizes (0: it does not take them): a block holds all of
+// a head's columns, so Dv * P <= 1024, and a lane at most 32 rows.
+RB_EXPORT int rb_delta_step_lanes(int D, int Dv, int n_rows) {
+  if (D <= 0 || Dv <= 0 || n_rows > 64) return 0;
+  int P = 32;
+  while (P > 1 && (Dv * P > 1024 || (D + P - 1) / P < 4)) P >>= 1;
+  if (Dv * P > 1024 || (D + P - 1) / P > 32) return 0;
+  return P;
+}
+
+// A decode step's delta rule in one launch (see the kernel).  proj: float32 rows [q | k | v | g | b | a] of the stacked
+// product; out: [rows, H * Dv] in float32 or bfloat16.
+RB_EXPORT int rb_delta_step(void* out, int out_dtype, const float* proj, int64_t ld, int g_off, int b_off, int a_off,
+                            const float* taps, const float* A_log, const float* dt_bias, const float* norm_w, float* state,
+                            float* tail, const int* tok_slot, const int* tok_pos, int n_rows, int H, int G, int D, int Dv, int K,
+                            float q_scale, float unit_eps, float norm_eps, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  const int P = rb_delta_step_lanes(D, Dv, n_rows);
+  RB_REQUIRE(P > 0 && H > 0 && G > 0 && H % G == 0 && K >= 1 && (K == 1 || tail != nullptr),
+             "rb_delta_step: sizes H=%d G=%d D=%d Dv=%d taps=%d rows=%d are not taken", H, G, D, Dv, K, n_rows);
+  const int per = (D + P - 1) / P;
+  const int threads = (Dv * P + 31) / 32 * 32;
+  const size_t smem = (size_t)(2 * D + Dv) * sizeof(float);
+  const dim3 grid(n_rows, H);
+  const int bf16 = out_dtype == RB_BF16 ? 1 : 0;
+  RB_REQUIRE(out_dtype == RB_BF16 || out_dtype == RB_F32, "rb_delta_step: unknown dtype %d", out_dtype);
+  if (per <= 16)
+    RB_LAUNCH("delta_step_kernel", (delta_step_kernel<16>), grid, threads, smem, stream, out, bf16, proj, ld, g_off, b_off, a_off, taps,
+              A_log, dt_bias, norm_w, state, tail, tok_slot, tok_pos, H, G, D, Dv, K, P, q_scale, unit_eps, norm_eps);
+  else
+    RB_LAUNCH("delta_step_kernel", (delta_step_kernel<32>), grid, threads, smem, stream, out, bf16, proj, ld, g_off, b_off, a_off, taps,
+              A_log, dt_bias, norm_w, state, tail, tok_slot, tok_pos, H, G, D, Dv, K, P, q_scale, unit_eps, norm_eps);
+  RB_CHECK_LAUNCH("rb_delta_step");
   return 0;
 }

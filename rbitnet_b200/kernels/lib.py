@@ -35,6 +35,8 @@ _SIGNATURES = {
     "rb_delta_prepare": [P, L, P, L, I, I, P, P, P, P, P, P, I, I, I, I, F, F, P],
     "rb_gated_delta_chunked": [P, P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "rb_gated_delta_chunked_supports": [I, I, ctypes.c_longlong, I],
+    "rb_delta_step": [P, I, P, L, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, F, P],
+    "rb_delta_step_lanes": [I, I, I],
     "rb_gated_delta": [P, P, L, P, P, P, P, P, P, P, I, I, I, I, I, P],
     "rb_layernorm": [P, I, P, P, P, I, I, F, P],
     "rb_add_rows": [P, P, ctypes.c_longlong, P],

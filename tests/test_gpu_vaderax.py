@@ -219,16 +219,18 @@ def test_dense_feed_forward(dtype, T):
     assert rel_err(part.forward(ctx, h.to(dtype).cuda()).cpu(), plain.dense_ff(h, w)) <= (1e-5 if dtype == torch.float32 else 2e-2)
 
 
-@pytest.mark.parametrize("chunks", [True, False])
+@pytest.mark.parametrize("chunks,one_launch", [(True, True), (False, False), (True, False)])
 @pytest.mark.parametrize("H,G,D,Dv,K", [(4, 2, 16, 24, 3), (1, 1, 40, 8, 1), (6, 3, 32, 64, 4), (2, 2, 128, 64, 2), (3, 1, 100, 33, 5),
                                         (2, 1, 8, 130, 2), (1, 1, 300, 20, 3), (2, 2, 600, 8, 2), (2, 1, 30, 16, 2)])
-def test_gated_delta_kernels(H, G, D, Dv, K, chunks):
+def test_gated_delta_kernels(H, G, D, Dv, K, chunks, one_launch):
     """Whole runs, portions and single tokens through the state and the convolution's ring; key sizes that one to
     thirty-two lanes hold; decays near one, so that the memory of the first tokens is still there at the end.  Runs of
-    several tokens in chunks of 32 (a run of 100 tokens ends inside its fourth chunk) and token by token."""
+    several tokens in chunks of 32 (a run of 100 tokens ends inside its fourth chunk) and token by token; single tokens
+    in the one kernel of a decode step and in the kernels of a prompt."""
     from rbitnet_b200.parts.delta import GatedDeltaRule
     ops = _ops(torch.float32)
     ops.delta_in_chunks = chunks
+    ops.fuse_delta_step = one_launch
     g = torch.Generator().manual_seed(H * 1000 + D)
     E, T = 32, 100
     part = GatedDeltaRule(E, H, G, D, Dv, K, norm_eps=1e-5)
