@@ -411,17 +411,21 @@ __global__ void __launch_bounds__(128) delta_chunk_prepare_kernel(
   }
 }
 
-// grid (runs, H, tiles of CT = 16 value columns), 128 threads.  Shared memory: two buffers of a chunk's W, q, k
+// grid (runs, H, tiles of CT = 16 value columns), 256 threads (eight warps: two per scheduler, so that one's
+// shared-memory loads run under the other's multiply-adds).  Shared memory: two buffers of a chunk's W, q, k
 // [32][D] each, M [32][32] and L [32], filled a chunk ahead with cp.async; the memory's tile S [D][16], U [32][16] and
 // the chunk's 2 x 32 exponentials.
 constexpr int CCT = 16;
+constexpr int SCAN_NT = 256;              // threads: 16 columns by SCAN_G groups of rows
+constexpr int SCAN_G = SCAN_NT / CCT;      // 16
+constexpr int SCAN_R = CH / SCAN_G;        // rows of a chunk per thread: 2
 __device__ __forceinline__ void cp_async16_or_zeros(void* dst, const void* src, bool real) {
   const int bytes = real ? 16 : 0;            // fewer source bytes than 16: the rest is filled with zeros
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes)
                : "memory");
 }
 
-__global__ void __launch_bounds__(128) delta_chunk_scan_kernel(
+__global__ void __launch_bounds__(SCAN_NT) delta_chunk_scan_kernel(
     float* __restrict__ o, const float* __restrict__ Wg, const float* __restrict__ Utg, const float* __restrict__ Mg,
     const float* __restrict__ Lg, const float* __restrict__ u, int64_t ldu, float* __restrict__ state,
     const int* __restrict__ seq_first, const int* __restrict__ seq_count, const int* __restrict__ run_chunk0,
@@ -434,7 +438,7 @@ __global__ void __launch_bounds__(128) delta_chunk_scan_kernel(
   float* Es = Us + CH * CCT;          // [32]: e^{L_i}
   float* Fs = Es + CH;                // [32]: e^{L_end - L_j}
   const int run = blockIdx.x, h = blockIdx.y, kvh = h / (H / G), col0 = blockIdx.z * CCT;
-  const int tid = threadIdx.x, c = tid & 15, g8 = tid >> 4;          // column of the tile; one of 8 groups of rows
+  const int tid = threadIdx.x, c = tid & 15, g8 = tid >> 4;          // column of the tile; one of SCAN_G groups of rows
   const bool live = col0 + c < Dv;
   rb_pdl_wait();
   const int first = seq_first[run], n = seq_count[run], chunk0 = run_chunk0[run];
@@ -449,21 +453,21 @@ __global__ void __launch_bounds__(128) delta_chunk_scan_kernel(
     float* Kc = Qs + CH * D;
     float* Ms = Kc + CH * D;
     float* Ls = Ms + CH * CH;
-    for (int i = tid; i < CH * D4; i += 128) {
+    for (int i = tid; i < CH * D4; i += SCAN_NT) {
       const int j = i / D4, d = (i - j * D4) << 2;
       cp_async16(Ws + j * D + d, Wg + item * CH * D + j * D + d);
       const float* row = u + (int64_t)(row0 + (j < m ? j : 0)) * ldu;
       cp_async16_or_zeros(Kc + j * D + d, row + k_off + d, j < m);
       cp_async16_or_zeros(Qs + j * D + d, row + q_off + d, j < m);
     }
-    for (int i = tid; i < CH * CH / 4; i += 128) cp_async16(Ms + 4 * i, Mg + item * CH * CH + 4 * i);
+    for (int i = tid; i < CH * CH / 4; i += SCAN_NT) cp_async16(Ms + 4 * i, Mg + item * CH * CH + 4 * i);
     if (tid < CH / 4) cp_async16(Ls + 4 * tid, Lg + item * CH + 4 * tid);
   };
   const int n_chunks = (n + CH - 1) / CH;
   copy_chunk(0, 0);
   cp_async_commit();
   float* mine = state + (((int64_t)slot * H + h) * Dv + col0) * D;      // [column][D]
-  for (int i = tid; i < D * CCT; i += 128) {
+  for (int i = tid; i < D * CCT; i += SCAN_NT) {
     const int cc = i / D, d = i - cc * D;
     Ss[d * CCT + cc] = col0 + cc < Dv ? mine[(int64_t)cc * D + d] : 0.f;
   }
@@ -485,20 +489,22 @@ __global__ void __launch_bounds__(128) delta_chunk_scan_kernel(
     const float* Ls = Ms + CH * CH;
     // asked for now, used after the products
     const float* Ut = Utg + item * CH * Dv;
-    float ut[4];
+    float ut[SCAN_R];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) ut[r] = live ? Ut[(int64_t)(g8 + 8 * r) * Dv + col0 + c] : 0.f;
+    for (int r = 0; r < SCAN_R; ++r) ut[r] = live ? Ut[(int64_t)(g8 + SCAN_G * r) * Dv + col0 + c] : 0.f;
     if (tid < CH) {
       Es[tid] = expf(Ls[tid]);
       Fs[tid] = expf(Ls[CH - 1] - Ls[tid]);
     }
-    // rows i = g8 + 8 r (r < 4) of column c:  W S and Q S
-    float ws[4] = {0.f, 0.f, 0.f, 0.f}, qs[4] = {0.f, 0.f, 0.f, 0.f};
+    // rows i = g8 + SCAN_G r (r < SCAN_R) of column c:  W S and Q S
+    float ws[SCAN_R], qs[SCAN_R];
+#pragma unroll
+    for (int r = 0; r < SCAN_R; ++r) ws[r] = qs[r] = 0.f;
     for (int d = 0; d < D; d += 4) {
       const float s0 = Ss[d * CCT + c], s1 = Ss[(d + 1) * CCT + c], s2 = Ss[(d + 2) * CCT + c], s3 = Ss[(d + 3) * CCT + c];
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int i = g8 + 8 * r;
+      for (int r = 0; r < SCAN_R; ++r) {
+        const int i = g8 + SCAN_G * r;
         const float4 w4 = *reinterpret_cast<const float4*>(Ws + i * D + d);
         const float4 q4 = *reinterpret_cast<const float4*>(Qs + i * D + d);
         ws[r] = fmaf(w4.x, s0, fmaf(w4.y, s1, fmaf(w4.z, s2, fmaf(w4.w, s3, ws[r]))));
@@ -506,19 +512,19 @@ __global__ void __launch_bounds__(128) delta_chunk_scan_kernel(
       }
     }
 #pragma unroll
-    for (int r = 0; r < 4; ++r) Us[(g8 + 8 * r) * CCT + c] = ut[r] - ws[r];
+    for (int r = 0; r < SCAN_R; ++r) Us[(g8 + SCAN_G * r) * CCT + c] = ut[r] - ws[r];
     __syncthreads();
     // the chunk's outputs: e^{L_i} (Q S)_i + sum_{j <= i} M_ij U_j
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int i = g8 + 8 * r;
+    for (int r = 0; r < SCAN_R; ++r) {
+      const int i = g8 + SCAN_G * r;
       float acc = Es[i] * qs[r];
       for (int j = 0; j <= i; ++j) acc = fmaf(Ms[i * CH + j], Us[j * CCT + c], acc);
       if (live && i < m) o[((int64_t)(row0 + i) * H + h) * Dv + col0 + c] = acc;
     }
-    // the memory moves on: S <- e^{L_end} S + sum_j e^{L_end - L_j} k_j U_j, rows d = g8 + 8 r of column c
+    // the memory moves on: S <- e^{L_end} S + sum_j e^{L_end - L_j} k_j U_j, rows d = d0 + g8 + SCAN_G r of column c
     const float keep = Es[CH - 1];
-    for (int d0 = 0; d0 < D; d0 += 64) {
+    for (int d0 = 0; d0 < D; d0 += 8 * SCAN_G) {
       float acc[8];
 #pragma unroll
       for (int r = 0; r < 8; ++r) acc[r] = 0.f;
@@ -526,20 +532,20 @@ __global__ void __launch_bounds__(128) delta_chunk_scan_kernel(
         const float uj = Fs[j] * Us[j * CCT + c];
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
-          const int d = d0 + g8 + 8 * r;
+          const int d = d0 + g8 + SCAN_G * r;
           if (d < D) acc[r] = fmaf(Kc[j * D + d], uj, acc[r]);
         }
       }
       // (every thread read the old S in the products above, before the barrier that followed them)
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
-        const int d = d0 + g8 + 8 * r;
+        const int d = d0 + g8 + SCAN_G * r;
         if (d < D) Ss[d * CCT + c] = fmaf(keep, Ss[d * CCT + c], acc[r]);
       }
     }
     __syncthreads();                  // before the copies of the chunk after the next overwrite this buffer, and U and the exponentials change
   }
-  for (int i = tid; i < D * CCT; i += 128) {
+  for (int i = tid; i < D * CCT; i += SCAN_NT) {
     const int cc = i / D, d = i - cc * D;
     if (col0 + cc < Dv) mine[(int64_t)cc * D + d] = Ss[d * CCT + cc];
   }
@@ -629,7 +635,7 @@ RB_EXPORT int rb_gated_delta_chunked(float* o, const float* u, int64_t ldu, cons
   RB_CHECK_LAUNCH("rb_gated_delta_chunked");
   const dim3 grid(n_runs, H, (Dv + CCT - 1) / CCT);
   RB_REQUIRE(grid.z <= 65535, "rb_gated_delta_chunked: too many columns");
-  RB_LAUNCH("delta_chunk_scan_kernel", (delta_chunk_scan_kernel), grid, 128, smem_b, stream, o, Wg, Utg, Mg, Lg, u, ldu, state,
+  RB_LAUNCH("delta_chunk_scan_kernel", (delta_chunk_scan_kernel), grid, SCAN_NT, smem_b, stream, o, Wg, Utg, Mg, Lg, u, ldu, state,
             seq_first, seq_count, run_chunk0, tok_slot, H, G, D, Dv);
   RB_CHECK_LAUNCH("rb_gated_delta_chunked");
   return 0;
